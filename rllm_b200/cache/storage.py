@@ -26,8 +26,8 @@ from ..parts.spec import KVPagesNeed, StateNeed
 
 
 def page_bytes(need: KVPagesNeed, page_size: int, elem_size: int) -> int:
-    """Bytes of one page of one run: K and V."""
-    return 2 * need.num_kv_heads * page_size * need.head_dim * elem_size
+    """Bytes of one page of one run: K and V (one buffer where keys serve as values)."""
+    return (2 if need.values else 1) * need.num_kv_heads * page_size * need.head_dim * elem_size
 
 
 class CacheStorage:
@@ -46,7 +46,7 @@ class CacheStorage:
                 if isinstance(need, KVPagesNeed):
                     shape = (pages_of[g] + 1, need.num_kv_heads, page_size, need.head_dim)
                     self.kv[run] = (torch.zeros(shape, dtype=dtype, device=device),
-                                    torch.zeros(shape, dtype=dtype, device=device))
+                                    torch.zeros(shape, dtype=dtype, device=device) if need.values else None)
                 elif isinstance(need, StateNeed):
                     self.state[run] = torch.zeros((max_seqs + 1,) + tuple(need.shape), dtype=torch.float32,
                                                   device=device)
@@ -85,11 +85,12 @@ class CacheStorage:
             for run in self.layout.owners[g]:
                 k, v = self.kv[run]
                 k[dst].copy_(k[src], non_blocking=True)
-                v[dst].copy_(v[src], non_blocking=True)
+                if v is not None:
+                    v[dst].copy_(v[src], non_blocking=True)
         src, dst = slots
         for t in self.state.values():
             t[dst].copy_(t[src], non_blocking=True)
 
     def num_bytes(self) -> int:
-        n = sum(k.numel() * k.element_size() * 2 for k, _ in self.kv.values())
+        n = sum(k.numel() * k.element_size() * (1 if v is None else 2) for k, v in self.kv.values())
         return n + sum(t.numel() * 4 for t in self.state.values())

@@ -57,6 +57,8 @@ def architecture_name(raw: Mapping[str, Any]) -> str:
     archs = raw.get("architectures")
     if isinstance(archs, (list, tuple)) and archs:
         name = str(archs[0])
+    elif isinstance(raw.get("architecture"), str) and raw["architecture"]:
+        name = raw["architecture"]               # configurations that name one architecture, not a list
     elif raw.get("model_type"):
         name = str(raw["model_type"])
     else:

@@ -36,7 +36,8 @@ NVCC_FLAGS = [
     "--expt-relaxed-constexpr",
 ]
 
-SOURCES = ["elementwise", "attention_simt", "attention_mma", "attention_tcgen05", "gemm_f32", "gemm_small_m", "gemm_tcgen05", "sampling", "weights_rng"]
+SOURCES = ["elementwise", "attention_simt", "attention_mma", "attention_tcgen05", "gemm_f32", "gemm_small_m", "gemm_tcgen05", "sampling", "weights_rng",
+           "layer_glue", "mingru", "latent_attention", "moe"]
 
 _lock = threading.Lock()
 _loaded: Dict[str, ctypes.CDLL] = {}

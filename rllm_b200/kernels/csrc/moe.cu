@@ -1,0 +1,244 @@
+// A feed-forward of routed experts.
+//   route:    z = W_r h in float32, s = softmax(z) over all experts; the `top` experts
+//             with the largest s (lowest index on ties) and their s, as they are.
+//   sort:     the (token, choice) pairs ordered by expert: offsets per expert, the
+//             pairs in that order, and a list of row tiles (expert, first row), all on
+//             the device, so that no size is read back to the host.
+//   gate_up:  per expert, y = act(W_gate h, W_up h) for its rows, with
+//             act(g, u) = g' sigmoid(alpha g') (u' + 1), g' = min(g, limit),
+//             u' = clamp(u, -limit, limit)  (alpha and limit are arguments).
+//   down:     per expert, W_down y, written to the pair's own row; the weighted sum
+//             over a token's pairs is taken by the kernel that reads the result, in
+//             the order of the choices.
+// A pair's result depends on its token and its expert only: not on the rows beside
+// it in a tile, not on the order of the pairs.
+#include "tile_gemm.cuh"
+#include <math.h>
+
+#define ROUTE_WARPS 4
+
+template <typename T>
+__global__ void __launch_bounds__(32 * ROUTE_WARPS)
+moe_route_kernel(const T* __restrict__ h, const T* __restrict__ wr, int* __restrict__ ids,
+                 float* __restrict__ weights, int T_tokens, int H, int E, int top) {
+  extern __shared__ float zs[];   // [ROUTE_WARPS][E]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t = blockIdx.x * ROUTE_WARPS + warp;
+  if (t >= T_tokens) return;
+  float* z = zs + warp * E;
+  const T* x = h + (size_t)t * H;
+  for (int e = 0; e < E; ++e) {
+    const T* w = wr + (size_t)e * H;
+    float part = 0.f;
+    for (int i = lane; i < H; i += 32) part = fmaf(to_f32(x[i]), to_f32(w[i]), part);
+    part = warp_sum(part);
+    if (lane == 0) z[e] = part;
+  }
+  __syncwarp();
+  float mx = -INFINITY;
+  for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
+  mx = warp_max(mx);
+  float sum = 0.f;
+  for (int e = lane; e < E; e += 32) sum += expf(z[e] - mx);
+  sum = warp_sum(sum);
+  __syncwarp();
+  for (int e = lane; e < E; e += 32) z[e] = expf(z[e] - mx) / sum;
+  __syncwarp();
+  for (int k = 0; k < top; ++k) {
+    float best = -1.f;
+    int bi = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      const float v = z[e];
+      if (v > best) { best = v; bi = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+    }
+    if (lane == 0) {
+      ids[(size_t)t * top + k] = bi;
+      weights[(size_t)t * top + k] = best;
+      z[bi] = -2.f;
+    }
+    __syncwarp();
+  }
+}
+
+RLLM_EXPORT int rllm_moe_route(const void* h, const void* wr, int* ids, float* weights, int T, int H, int E,
+                               int top, int dtype, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (H <= 0 || E <= 0 || top <= 0 || top > E || E > 2048) return RLLM_E_BADARG;
+  const unsigned blocks = (unsigned)((T + ROUTE_WARPS - 1) / ROUTE_WARPS);
+  const size_t smem = (size_t)ROUTE_WARPS * E * sizeof(float);
+  RLLM_DISPATCH_DTYPE(dtype, TT, (moe_route_kernel<TT><<<blocks, 32 * ROUTE_WARPS, smem, stream>>>(
+      (const TT*)h, (const TT*)wr, ids, weights, T, H, E, top)));
+  RLLM_LAUNCH_CHECK();
+  return 0;
+}
+
+// meta: [0] number of tiles.  offsets [E + 1].  sorted [P]: pair indices by expert.
+// tile_expert, tile_row0 [max_tiles].
+__global__ void __launch_bounds__(1024)
+moe_sort_kernel(const int* __restrict__ ids, int P, int E, int bm, int* __restrict__ offsets,
+                int* __restrict__ sorted, int* __restrict__ tile_expert, int* __restrict__ tile_row0,
+                int* __restrict__ meta) {
+  extern __shared__ int sh[];      // counts [E], start [E + 1], tile_start [E + 1], cursor [E]
+  int* cnt = sh;
+  int* start = cnt + E;
+  int* tstart = start + E + 1;
+  int* cur = tstart + E + 1;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) { cnt[e] = 0; cur[e] = 0; }
+  __syncthreads();
+  for (int p = threadIdx.x; p < P; p += blockDim.x) atomicAdd(&cnt[ids[p]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int a = 0, b = 0;
+    for (int e = 0; e < E; ++e) {
+      start[e] = a; tstart[e] = b;
+      a += cnt[e];
+      b += (cnt[e] + bm - 1) / bm;
+    }
+    start[E] = a; tstart[E] = b;
+    meta[0] = b;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e <= E; e += blockDim.x) offsets[e] = start[e];
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    const int n = tstart[e + 1] - tstart[e];
+    for (int i = 0; i < n; ++i) {
+      tile_expert[tstart[e] + i] = e;
+      tile_row0[tstart[e] + i] = start[e] + i * bm;
+    }
+  }
+  for (int p = threadIdx.x; p < P; p += blockDim.x) {
+    const int e = ids[p];
+    sorted[start[e] + atomicAdd(&cur[e], 1)] = p;
+  }
+}
+
+RLLM_EXPORT int rllm_moe_sort(const int* ids, int P, int E, int bm, int* offsets, int* sorted, int* tile_expert,
+                              int* tile_row0, int* meta, cudaStream_t stream) {
+  if (P <= 0) return 0;
+  if (E <= 0 || E > 2048 || (bm != 16 && bm != 64)) return RLLM_E_BADARG;
+  const size_t smem = (size_t)(4 * E + 2) * sizeof(int);
+  moe_sort_kernel<<<1, 1024, smem, stream>>>(ids, P, E, bm, offsets, sorted, tile_expert, tile_row0, meta);
+  RLLM_LAUNCH_CHECK();
+  return 0;
+}
+
+// y[row, n] = act(h[token(row)] . Wg[e][n], h[token(row)] . Wu[e][n]);  w: [E, 2 F, H], gate rows then up rows
+template <typename T, int BM>
+__global__ void __launch_bounds__(TG_THREADS)
+moe_gate_up_kernel(const T* __restrict__ h, const T* __restrict__ w, T* __restrict__ y,
+                   const int* __restrict__ offsets, const int* __restrict__ sorted,
+                   const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
+                   const int* __restrict__ meta, int H, int F, int top, float limit, float alpha) {
+  __shared__ TileGemmSmem<BM> sm;
+  const int tile = blockIdx.y;
+  if (tile >= meta[0]) return;
+  const int e = tile_expert[tile], r0 = tile_row0[tile], rend = offsets[e + 1];
+  const int n0 = blockIdx.x * TG_BN;
+  if (threadIdx.x < BM) {
+    const int r = r0 + threadIdx.x;
+    sm.rows[threadIdx.x] = (r < rend) ? (const void*)(h + (size_t)(sorted[r] / top) * H) : nullptr;
+  }
+  __syncthreads();
+  float g[BM / 16][4], u[BM / 16][4];
+  const T* we = w + (size_t)e * 2 * F * H;
+  tile_gemm_accumulate<T, BM, false>(sm, we, H, n0, F, H, g);
+  tile_gemm_accumulate<T, BM, false>(sm, we + (size_t)F * H, H, n0, F, H, u);
+  const int tm = (threadIdx.x / 16) * (BM / 16), tn = (threadIdx.x % 16) * 4;
+#pragma unroll
+  for (int i = 0; i < BM / 16; ++i) {
+    const int r = r0 + tm + i;
+    if (r >= rend) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tn + j;
+      if (n >= F) continue;
+      const float gg = fminf(g[i][j], limit), uu = fminf(fmaxf(u[i][j], -limit), limit);
+      y[(size_t)r * F + n] = from_f32<T>(gg * (1.0f / (1.0f + expf(-alpha * gg))) * (uu + 1.0f));
+    }
+  }
+}
+
+// out[pair(row), n] = y[row] . Wd[e][n];  w: [E, H, F]
+template <typename T, int BM>
+__global__ void __launch_bounds__(TG_THREADS)
+moe_down_kernel(const T* __restrict__ y, const T* __restrict__ w, T* __restrict__ out,
+                const int* __restrict__ offsets, const int* __restrict__ sorted,
+                const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
+                const int* __restrict__ meta, int H, int F) {
+  __shared__ TileGemmSmem<BM> sm;
+  const int tile = blockIdx.y;
+  if (tile >= meta[0]) return;
+  const int e = tile_expert[tile], r0 = tile_row0[tile], rend = offsets[e + 1];
+  const int n0 = blockIdx.x * TG_BN;
+  if (threadIdx.x < BM) {
+    const int r = r0 + threadIdx.x;
+    sm.rows[threadIdx.x] = (r < rend) ? (const void*)(y + (size_t)r * F) : nullptr;
+  }
+  __syncthreads();
+  float acc[BM / 16][4];
+  tile_gemm_accumulate<T, BM, false>(sm, w + (size_t)e * H * F, F, n0, H, F, acc);
+  const int tm = (threadIdx.x / 16) * (BM / 16), tn = (threadIdx.x % 16) * 4;
+#pragma unroll
+  for (int i = 0; i < BM / 16; ++i) {
+    const int r = r0 + tm + i;
+    if (r >= rend) continue;
+    const int pair = sorted[r];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tn + j;
+      if (n < H) out[(size_t)pair * H + n] = from_f32<T>(acc[i][j]);
+    }
+  }
+}
+
+// out[t, :] = sum_k c[t, k] y[t * K + k, :], the k terms in order
+template <typename T>
+__global__ void weighted_slot_sum_kernel(const T* __restrict__ y, const float* __restrict__ c, T* __restrict__ out,
+                                         int slots, int H, long long total) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const long long t = idx / H;
+  const int i = (int)(idx - t * H);
+  float v = 0.f;
+  for (int k = 0; k < slots; ++k) v = fmaf(c[t * slots + k], to_f32(y[((size_t)t * slots + k) * H + i]), v);
+  out[idx] = from_f32<T>(v);
+}
+
+RLLM_EXPORT int rllm_weighted_slot_sum(const void* y, const float* c, void* out, int T, int slots, int H,
+                                       int dtype, cudaStream_t stream) {
+  const long long total = (long long)T * H;
+  if (total <= 0) return 0;
+  if (slots <= 0) return RLLM_E_BADARG;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  RLLM_DISPATCH_DTYPE(dtype, TT, (weighted_slot_sum_kernel<TT><<<blocks, 256, 0, stream>>>(
+      (const TT*)y, c, (TT*)out, slots, H, total)));
+  RLLM_LAUNCH_CHECK();
+  return 0;
+}
+
+RLLM_EXPORT int rllm_moe_experts(const void* h, const void* w_gate_up, const void* w_down, void* y, void* out,
+                                 const int* offsets, const int* sorted, const int* tile_expert,
+                                 const int* tile_row0, const int* meta, int max_tiles, int bm, int H, int F,
+                                 int top, float limit, float alpha, int dtype, cudaStream_t stream) {
+  if (max_tiles <= 0) return 0;
+  if (H <= 0 || F <= 0 || top <= 0 || (bm != 16 && bm != 64)) return RLLM_E_BADARG;
+  if (max_tiles > 65535) return RLLM_E_UNSUPPORTED;
+  dim3 g1((F + TG_BN - 1) / TG_BN, max_tiles), g2((H + TG_BN - 1) / TG_BN, max_tiles);
+#define MOE_LAUNCH(T_, BM_)                                                                                  \
+  do {                                                                                                       \
+    moe_gate_up_kernel<T_, BM_><<<g1, TG_THREADS, 0, stream>>>((const T_*)h, (const T_*)w_gate_up, (T_*)y,    \
+        offsets, sorted, tile_expert, tile_row0, meta, H, F, top, limit, alpha);                             \
+    moe_down_kernel<T_, BM_><<<g2, TG_THREADS, 0, stream>>>((const T_*)y, (const T_*)w_down, (T_*)out, offsets, \
+        sorted, tile_expert, tile_row0, meta, H, F);                                                         \
+  } while (0)
+  RLLM_DISPATCH_DTYPE(dtype, TT, { if (bm == 16) MOE_LAUNCH(TT, 16); else MOE_LAUNCH(TT, 64); });
+#undef MOE_LAUNCH
+  RLLM_LAUNCH_CHECK();
+  return 0;
+}

@@ -615,3 +615,229 @@ def logprobs(logits: torch.Tensor, tokens: torch.Tensor, top_n: int):
                              _ptr(lp), _ptr(ids) if top_n else c_void_p(0), _ptr(vals) if top_n else c_void_p(0),
                              _stream()), "logprobs")
     return lp, ids, vals
+
+
+# ---------------------------------------------------------------------------
+# gated, normalised sublayer results and the depth-weighted stream (layer_glue.cu)
+# ---------------------------------------------------------------------------
+def gated_postnorm_add(x_in: torch.Tensor, x_out: torch.Tensor, y: torch.Tensor, gate: torch.Tensor,
+                       gate_bias: torch.Tensor, norm_weight: torch.Tensor, eps: float,
+                       slot_weights: Optional[torch.Tensor] = None,
+                       next_weight: Optional[torch.Tensor] = None, next_eps: float = 0.0) -> Optional[torch.Tensor]:
+    """x_out = x_in + rmsnorm(v) * norm_weight with v = y * sigmoid(gate + gate_bias); x float32 [T, H]
+    (x_out may be x_in).  ``slot_weights`` float32 [T, K]: y is [T * K, H] and a token's K rows are added
+    with these factors first.  ``gate`` [T, H] may be a column slice (row stride >= H).  With
+    ``next_weight`` the RMS norm of the new x under that weight is returned in the activation dtype."""
+    lib = build.load_library("layer_glue")
+    T, H = x_in.shape
+    assert x_in.dtype is torch.float32 and x_out.dtype is torch.float32 and x_out.shape == x_in.shape
+    _contig(x_in, "x_in"); _contig(x_out, "x_out"); _contig(y, "y")
+    slots = 1
+    if slot_weights is not None:
+        assert slot_weights.dtype is torch.float32 and slot_weights.shape[0] == T
+        _contig(slot_weights, "slot_weights")
+        slots = slot_weights.shape[1]
+    assert y.shape == (T * slots, H) and gate.shape == (T, H) and gate.dtype is y.dtype and gate.stride(1) == 1
+    assert gate_bias.dtype is norm_weight.dtype and gate_bias.numel() == H and norm_weight.numel() == H
+    nxt = None
+    if next_weight is not None:
+        assert next_weight.dtype is norm_weight.dtype and next_weight.numel() == H
+        nxt = torch.empty((T, H), dtype=y.dtype, device=y.device)
+    _check(lib.rllm_gated_postnorm_add(_ptr(x_in), _ptr(x_out), _ptr(y), c_int(slots), _ptr(slot_weights),
+                                       _ptr(gate), c_int(gate.stride(0) if T > 1 else max(H, gate.stride(0))),
+                                       _ptr(gate_bias), _ptr(norm_weight), c_float(eps), _ptr(next_weight),
+                                       _ptr(nxt), c_float(next_eps), c_int(T), c_int(H),
+                                       c_int(dtype_code(y.dtype)), c_int(dtype_code(norm_weight.dtype)),
+                                       _stream()), "gated_postnorm_add")
+    return nxt
+
+
+def depth_average(history: torch.Tensor, levels: int, coeff: torch.Tensor, stream_out: Optional[torch.Tensor],
+                  norm_weight: Optional[torch.Tensor], eps: float, act_dtype: torch.dtype,
+                  rows: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """s = sum_j coeff[j] * history[j] over the first ``levels`` levels; history float32 [L, T, H].
+    Writes s to ``stream_out`` (float32 [T, H]) if given and returns rmsnorm(s) * norm_weight in
+    ``act_dtype`` if a weight is given.  ``rows`` (int32 [R]): only these rows (no ``stream_out`` then)."""
+    lib = build.load_library("layer_glue")
+    L, T, H = history.shape
+    assert history.dtype is torch.float32 and 1 <= levels <= L and coeff.numel() == levels
+    _contig(history, "history"); _contig(coeff, "coeff")
+    R = T if rows is None else rows.numel()
+    if rows is not None:
+        assert rows.dtype is torch.int32 and stream_out is None
+    if stream_out is not None:
+        assert stream_out.dtype is torch.float32 and stream_out.shape == (T, H)
+        _contig(stream_out, "stream_out")
+    out = None
+    if norm_weight is not None:
+        assert norm_weight.dtype is coeff.dtype and norm_weight.numel() == H
+        out = torch.empty((R, H), dtype=act_dtype, device=history.device)
+    _check(lib.rllm_depth_average(_ptr(history), c_longlong(history.stride(0)), c_int(levels), _ptr(coeff),
+                                  _ptr(rows), _ptr(stream_out), _ptr(norm_weight), _ptr(out), c_float(eps),
+                                  c_int(R), c_int(H), c_int(dtype_code(act_dtype)),
+                                  c_int(dtype_code(coeff.dtype)), _stream()), "depth_average")
+    return out
+
+
+# ---------------------------------------------------------------------------
+# minGRU (mingru.cu)
+# ---------------------------------------------------------------------------
+def mingru_scan(zxg: torch.Tensor, bias_z: torch.Tensor, bias_x: torch.Tensor, state: torch.Tensor,
+                q_start: torch.Tensor, slots: torch.Tensor, num_seqs: int, out: torch.Tensor,
+                err: torch.Tensor) -> None:
+    """zxg [T, >= 3 W]: a token's z, x and g projections side by side; state float32 [slots, W], updated in
+    place for the sequences' slots; out [T, W] = S_t * silu(g)."""
+    lib = build.load_library("mingru")
+    T, W = out.shape
+    assert zxg.shape[0] == T and zxg.stride(1) == 1 and zxg.shape[1] >= 3 * W and out.dtype is zxg.dtype
+    assert state.dtype is torch.float32 and state.shape[1] == W
+    assert bias_z.dtype is bias_x.dtype and bias_z.numel() == W and bias_x.numel() == W
+    _contig(out, "out"); _contig(state, "state")
+    _check(lib.rllm_mingru_scan(_ptr(zxg), c_int(zxg.stride(0)), _ptr(bias_z), _ptr(bias_x), _ptr(state),
+                                _ptr(q_start), _ptr(slots), c_int(state.shape[0]), _ptr(out), c_int(num_seqs),
+                                c_int(W), c_int(dtype_code(out.dtype)), c_int(dtype_code(bias_z.dtype)),
+                                _ptr(err), _stream()), "mingru_scan")
+
+
+# ---------------------------------------------------------------------------
+# attention through a latent (latent_attention.cu)
+# ---------------------------------------------------------------------------
+def latent_prep(a: torch.Tensor, q_rank: int, kv_rank: int, rot: int, rot_dims: int, wq: torch.Tensor,
+                wkv: Optional[torch.Tensor], eps: float, cq: torch.Tensor, cache: Optional[torch.Tensor],
+                block_table: Optional[torch.Tensor], positions: torch.Tensor, token_seq: torch.Tensor,
+                inv_freq: Optional[torch.Tensor], err: torch.Tensor) -> None:
+    """a [T, q_rank (+ kv_rank + rot)]: the down projections of a token side by side.  cq [T, q_rank] =
+    rmsnorm(a[:, :q_rank]) * wq.  With a cache ([pages, 1, page_size, kv_rank + rot]) the token's row is
+    written: rmsnorm of the next kv_rank values times wkv, then the last rot values, the first rot_dims
+    of them rotated by position (pairs 2i, 2i+1)."""
+    lib = build.load_library("latent_attention")
+    T = a.shape[0]
+    write = cache is not None
+    assert a.stride(1) == 1 and cq.shape == (T, q_rank) and cq.dtype is a.dtype
+    _contig(cq, "cq")
+    if write:
+        assert a.shape[1] == q_rank + kv_rank + rot and cache.dtype is a.dtype and cache.shape[3] == kv_rank + rot
+        assert cache.shape[1] == 1 and wkv is not None and wkv.dtype is wq.dtype
+        _contig(cache, "cache"); _contig(block_table, "block_table")
+        if rot_dims:
+            assert inv_freq is not None and inv_freq.dtype is torch.float64 and inv_freq.numel() == rot_dims // 2
+        pages, page_size, max_blocks = cache.shape[0], cache.shape[2], block_table.shape[1]
+    else:
+        pages = page_size = max_blocks = 0
+    _check(lib.rllm_latent_prep(_ptr(a), c_int(a.stride(0)), c_int(q_rank), c_int(kv_rank), c_int(rot),
+                                c_int(rot_dims), _ptr(wq), _ptr(wkv), c_float(eps), _ptr(cq), _ptr(cache),
+                                _ptr(block_table), c_int(max_blocks), _ptr(positions), _ptr(token_seq),
+                                _ptr(inv_freq), c_int(page_size), c_int(pages), c_int(1 if write else 0),
+                                c_int(T), c_int(dtype_code(a.dtype)), c_int(dtype_code(wq.dtype)), _ptr(err),
+                                _stream()), "latent_prep")
+
+
+def latent_q_rot(q: torch.Tensor, qt: torch.Tensor, positions: torch.Tensor, inv_freq: Optional[torch.Tensor],
+                 heads: int, dim: int, rot: int, rot_dims: int, kv_rank: int) -> None:
+    """qt[t, h, kv_rank:] = q[t, h, dim:] with its first rot_dims values rotated by position."""
+    lib = build.load_library("latent_attention")
+    T = q.shape[0]
+    assert q.shape == (T, heads * (dim + rot)) and qt.shape == (T, heads * (kv_rank + rot)) and qt.dtype is q.dtype
+    _contig(q, "q"); _contig(qt, "qt")
+    _check(lib.rllm_latent_q_rot(_ptr(q), _ptr(qt), _ptr(positions), _ptr(inv_freq), c_int(T), c_int(heads),
+                                 c_int(dim), c_int(rot), c_int(rot_dims), c_int(kv_rank),
+                                 c_int(dtype_code(q.dtype)), _stream()), "latent_q_rot")
+
+
+def head_gemm(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, b_kn: bool) -> None:
+    """c[m, h, :] = a[m, h, :] . b[h] for every head h.  a [M, heads, K], c [M, heads, N]: views with unit
+    stride in the last dim; b [heads, K, N] (``b_kn``) or [heads, N, K], contiguous."""
+    lib = build.load_library("latent_attention")
+    M, heads, K = a.shape
+    N = c.shape[2]
+    assert c.shape[:2] == (M, heads) and a.stride(2) == 1 and c.stride(2) == 1 and a.dtype is b.dtype is c.dtype
+    assert b.shape == ((heads, K, N) if b_kn else (heads, N, K))
+    _contig(b, "b")
+    _check(lib.rllm_head_gemm(_ptr(a), c_longlong(a.stride(0)), c_longlong(a.stride(1)), _ptr(b),
+                              c_longlong(b.stride(1)), c_longlong(b.stride(0)), c_int(1 if b_kn else 0), _ptr(c),
+                              c_longlong(c.stride(0)), c_longlong(c.stride(1)), c_int(M), c_int(N), c_int(K),
+                              c_int(heads), c_int(dtype_code(a.dtype)), _stream()), "head_gemm")
+
+
+def latent_attention_simt(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
+                          positions: torch.Tensor, token_seq: torch.Tensor, heads: int, dk: int, dv: int,
+                          window: int, scale: float, sink: Optional[torch.Tensor], err: torch.Tensor) -> None:
+    """q [T, heads * dk], cache [pages, 1, page_size, dk], out [T, heads * dv]: softmax(q . row * scale) over
+    the visible rows (``window`` 0: all up to the query's position), times the rows' first dv values.
+    ``sink`` float32 [heads]: exp(sink[h]) joins the denominator."""
+    lib = build.load_library("latent_attention")
+    T = q.shape[0]
+    assert q.shape == (T, heads * dk) and out.shape == (T, heads * dv) and cache.shape[3] == dk
+    assert cache.dtype is q.dtype and out.dtype is q.dtype
+    _contig(q, "q"); _contig(out, "out"); _contig(cache, "cache"); _contig(block_table, "block_table")
+    if sink is not None:
+        assert sink.dtype is torch.float32 and sink.numel() == heads
+    _check(lib.rllm_latent_attention_simt(_ptr(q), _ptr(out), _ptr(cache), c_int(dtype_code(q.dtype)),
+                                          _ptr(block_table), c_int(block_table.shape[1]), _ptr(positions),
+                                          _ptr(token_seq), c_int(T), c_int(heads), c_int(dk), c_int(dv),
+                                          c_int(cache.shape[2]), c_int(cache.shape[0]), c_int(window),
+                                          c_float(scale), _ptr(sink), _ptr(err), _stream()),
+           "latent_attention_simt")
+
+
+# ---------------------------------------------------------------------------
+# routed experts (moe.cu)
+# ---------------------------------------------------------------------------
+MOE_SMALL_PAIRS = 64      # up to this many (token, expert) pairs a step the expert products use row tiles of 16
+
+
+def moe_route(h: torch.Tensor, w_router: torch.Tensor, top: int):
+    """(ids int32 [T, top], scores float32 [T, top]): softmax over all experts of the float32 logits
+    h . w_router^T, the ``top`` largest in falling order (lowest index first among equals)."""
+    lib = build.load_library("moe")
+    T, H = h.shape
+    E = w_router.shape[0]
+    assert w_router.shape == (E, H) and w_router.dtype is h.dtype
+    _contig(h, "h"); _contig(w_router, "w_router")
+    ids = torch.empty((T, top), dtype=torch.int32, device=h.device)
+    scores = torch.empty((T, top), dtype=torch.float32, device=h.device)
+    _check(lib.rllm_moe_route(_ptr(h), _ptr(w_router), _ptr(ids), _ptr(scores), c_int(T), c_int(H), c_int(E),
+                              c_int(top), c_int(dtype_code(h.dtype)), _stream()), "moe_route")
+    return ids, scores
+
+
+def moe_experts(h: torch.Tensor, ids: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, limit: float,
+                alpha: float) -> torch.Tensor:
+    """out [T * top, H]: row t * top + k is expert ids[t, k] applied to h[t]:
+    W_down (g' sigmoid(alpha g') (u' + 1)), g' = min(W_gate h, limit), u' = clamp(W_up h, +-limit).
+    w_gate_up [E, 2 F, H] (gate rows, then up rows), w_down [E, H, F]."""
+    lib = build.load_library("moe")
+    T, H = h.shape
+    top = ids.shape[1]
+    E, F2, _ = w_gate_up.shape
+    F = F2 // 2
+    assert w_gate_up.shape == (E, 2 * F, H) and w_down.shape == (E, H, F) and ids.shape == (T, top)
+    assert w_gate_up.dtype is h.dtype and w_down.dtype is h.dtype and ids.dtype is torch.int32
+    _contig(h, "h"); _contig(w_gate_up, "w_gate_up"); _contig(w_down, "w_down"); _contig(ids, "ids")
+    P = T * top
+    bm = 16 if P <= MOE_SMALL_PAIRS else 64
+    max_tiles = min(P, -(-P // bm) + E)
+    meta = torch.empty(1 + (E + 1) + P + 2 * max_tiles, dtype=torch.int32, device=h.device)
+    m_tiles, offsets, sorted_pairs = meta[0:1], meta[1:E + 2], meta[E + 2:E + 2 + P]
+    tile_expert = meta[E + 2 + P:E + 2 + P + max_tiles]
+    tile_row0 = meta[E + 2 + P + max_tiles:]
+    _check(lib.rllm_moe_sort(_ptr(ids), c_int(P), c_int(E), c_int(bm), _ptr(offsets), _ptr(sorted_pairs),
+                             _ptr(tile_expert), _ptr(tile_row0), _ptr(m_tiles), _stream()), "moe_sort")
+    y = torch.empty((P, F), dtype=h.dtype, device=h.device)
+    out = torch.empty((P, H), dtype=h.dtype, device=h.device)
+    _check(lib.rllm_moe_experts(_ptr(h), _ptr(w_gate_up), _ptr(w_down), _ptr(y), _ptr(out), _ptr(offsets),
+                                _ptr(sorted_pairs), _ptr(tile_expert), _ptr(tile_row0), _ptr(m_tiles),
+                                c_int(max_tiles), c_int(bm), c_int(H), c_int(F), c_int(top), c_float(limit),
+                                c_float(alpha), c_int(dtype_code(h.dtype)), _stream()), "moe_experts")
+    return out
+
+
+def weighted_slot_sum(y: torch.Tensor, coeff: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t] = sum_k coeff[t, k] * y[t * K + k]; y [T * K, H], coeff float32 [T, K], out [T, H]."""
+    lib = build.load_library("moe")
+    T, H = out.shape
+    K = coeff.shape[1]
+    assert y.shape == (T * K, H) and coeff.shape == (T, K) and coeff.dtype is torch.float32 and y.dtype is out.dtype
+    _contig(y, "y"); _contig(coeff, "coeff"); _contig(out, "out")
+    _check(lib.rllm_weighted_slot_sum(_ptr(y), _ptr(coeff), _ptr(out), c_int(T), c_int(K), c_int(H),
+                                      c_int(dtype_code(out.dtype)), _stream()), "weighted_slot_sum")

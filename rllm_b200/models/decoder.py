@@ -46,14 +46,22 @@ class DecoderModel:
         self.blocks = []
         for ls in spec.layers:
             mixer = part_registry.build_part("mixer", ls.mixer, prefix=ls.prefix + _sub(ls.mixer))
-            ffn = part_registry.build_part("feed_forward", ls.ffn, prefix=ls.prefix + _sub(ls.ffn))
+            ffn = None if ls.ffn is None else \
+                part_registry.build_part("feed_forward", ls.ffn, prefix=ls.prefix + _sub(ls.ffn))
             norms = [part_registry.build_part("norm", n, prefix=ls.prefix) for n in ls.norms]
             if ls.block not in part_registry.BLOCKS:
                 raise KeyError(f"no block arrangement {ls.block!r}; known: {sorted(part_registry.BLOCKS)}")
-            self.blocks.append(part_registry.BLOCKS[ls.block](mixer, ffn, norms))
+            if ls.block_params is not None:
+                # an arrangement with sizes, constants and tensors of its own
+                self.blocks.append(part_registry.BLOCKS[ls.block](mixer, ffn, norms, spec=ls.block_params,
+                                                                  prefix=ls.prefix))
+            else:
+                self.blocks.append(part_registry.BLOCKS[ls.block](mixer, ffn, norms))
         self.final_norm = part_registry.build_part("norm", spec.final_norm)
         self.head = OutputHead(spec.head)
         self.layout = self._cache_layout()
+        # blocks whose stream is a weighted sum of all earlier results: how many results the model keeps
+        self.depth_levels = max((int(getattr(b, "depth_levels", 0) or 0) for b in self.blocks), default=0)
         self.dtype: Optional[torch.dtype] = None
         self.device: Optional[torch.device] = None
 
@@ -102,10 +110,17 @@ class DecoderModel:
                 run_group.append(None)
                 run_owner.append(None)
                 continue
-            owner_need = self.blocks[self.spec.order[run.cache].layer].mixer.cache_need()
-            if run.cache != i and owner_need != need:
-                raise ValueError(f"order[{i}] reads the cache of run {run.cache}, whose mixer keeps "
-                                 f"{owner_need}, not {need}")
+            # a slot keeps what its owner and every run that reads it need: the same rows, the widest window
+            for j, other in enumerate(self.spec.order):
+                if other.cache != run.cache or j == i:
+                    continue
+                theirs = self.blocks[other.layer].mixer.cache_need()
+                wide = need.widened(theirs) if hasattr(need, "widened") and type(theirs) is type(need) else \
+                    (need if theirs == need else None)
+                if wide is None:
+                    raise ValueError(f"order[{i}] and order[{j}] use cache slot {run.cache} but keep "
+                                     f"{need} and {theirs}")
+                need = wide
             if need not in groups:
                 groups.append(need)
                 owners.append([])
@@ -122,7 +137,14 @@ class DecoderModel:
         """Logits float32 [R, vocab] at the rows ``logit_rows`` (int32 indices
         into this step's tokens).  ``storage.view(run_index)`` gives a run's
         cache view."""
-        h = self.embedding.forward(token_ids, ctx.err)
+        if self.depth_levels:
+            # level 0 is the embedding's output, level i + 1 the result of run i; the blocks fill and read it
+            hist = torch.empty((self.depth_levels, token_ids.numel(), self.spec.hidden_size), dtype=torch.float32,
+                               device=token_ids.device)
+            ctx.extras["depth_history"] = hist
+            h = self.embedding.forward(token_ids, ctx.err, out=hist[0])
+        else:
+            h = self.embedding.forward(token_ids, ctx.err)
         pending = None
         order = self.spec.order
         for i, run in enumerate(order):

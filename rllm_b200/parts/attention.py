@@ -61,6 +61,8 @@ class PagedAttention(Mixer):
         pos = p.get("position")
         self.position = build_part("position_encoding", pos if pos is not None else PartSpec.of("none"),
                                    prefix=prefix)
+        if getattr(self.position, "interleaved", False):
+            raise ValueError("this mixer's kernels rotate halves; an interleaved rotation is not among them")
         self.w_qkv: Optional[torch.Tensor] = None
         self.w_o: Optional[torch.Tensor] = None
 

@@ -94,6 +94,17 @@ class RowSumsq:
 
 
 @dataclass
+class NormedRows:
+    """h is complete, and ``x`` [T, H] is already its norm under the weight ``by`` and
+    ``eps`` (activation dtype): a block whose first norm has that weight and eps
+    reads ``x`` instead of running the norm; any other reader ignores it."""
+
+    x: torch.Tensor
+    by: torch.Tensor
+    eps: float
+
+
+@dataclass
 class ScaledRows:
     """An RMS-normalised activation that has not been divided by its rows' root mean
     square yet: ``x`` = h * weight, ``parts`` and ``eps`` give the rows' factors
@@ -118,10 +129,11 @@ class ScaledRows:
 
 @dataclass
 class KVCacheView:
-    """The pages of one run's attention: K and V [pages, nkv, page_size, d]."""
+    """The pages of one run's attention: K and V [pages, nkv, page_size, d]; ``v`` is None
+    where a token keeps one row that serves as both (``KVPagesNeed.values`` False)."""
 
     k: torch.Tensor
-    v: torch.Tensor
+    v: Optional[torch.Tensor]
     group: int
     writes: bool
 

@@ -48,15 +48,15 @@ class PreNormBlock:
         if self._fused(h.shape[0], ctx):
             xn = self.norms[0].scaled_input(pending) if isinstance(pending, RowSumsq) else None
             if xn is None:
-                if pending is None or isinstance(pending, RowSumsq):
+                if not isinstance(pending, torch.Tensor):
                     xn = self.norms[0].forward(h, ctx.act_dtype)
                 else:
                     xn = self.norms[0].add_forward(h, pending)
             stats = self.mixer.forward(xn, ctx, cache, residual=(h, self.norms[1]))
             stats = self.ffn.forward(self.norms[1].scaled_input(stats), residual=(h, next_norm))
             return h, stats
-        if isinstance(pending, RowSumsq):
-            pending = None                      # h is complete
+        if not isinstance(pending, torch.Tensor):
+            pending = None                      # h is complete (whatever a block ahead prepared beside it)
         if pending is None:
             xn = self.norms[0].forward(h, ctx.act_dtype)
         else:

@@ -34,8 +34,9 @@ class TokenEmbedding(Part):
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
         self.weight = tensors[self.name]
 
-    def forward(self, token_ids: torch.Tensor, err: torch.Tensor) -> torch.Tensor:
-        out = torch.empty((token_ids.numel(), self.hidden), dtype=torch.float32, device=token_ids.device)
+    def forward(self, token_ids: torch.Tensor, err: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if out is None:
+            out = torch.empty((token_ids.numel(), self.hidden), dtype=torch.float32, device=token_ids.device)
         ops.embedding(token_ids, self.weight, out, err)
         return out
 

@@ -48,6 +48,9 @@ def rotary_frequencies(rotary_dim: int, theta: float, scaling: Optional[dict]) -
 @register_part("position_encoding", "rotary")
 class Rotary(PositionEncoding):
     """params: head_dim, rotary_dim (<= head_dim, even), theta, scaling (dict or None),
+    interleaved (False: dimension i is paired with i + rotary_dim / 2, the rotate-half convention;
+    True: dimension 2i with 2i + 1; the frequencies are the same, and a mixer reads the flag: the
+    kernels that ``fused_rotary`` serves rotate halves, so a mixer must not hand them an interleaved part),
     ignored_tensors (names below the mixer's prefix under which checkpoints of the family store
     a frequency table; it is computed here, so such a tensor is passed over)."""
     graph_safe = True
@@ -59,6 +62,7 @@ class Rotary(PositionEncoding):
         self.rotary_dim = int(p.get("rotary_dim", self.head_dim))
         if self.rotary_dim % 2 or not 0 < self.rotary_dim <= self.head_dim:
             raise ValueError(f"rotary_dim {self.rotary_dim} must be even and within head_dim {self.head_dim}")
+        self.interleaved = bool(p.get("interleaved", False))
         scaling = p.get("scaling")
         self.scaling = dict(scaling) if scaling else None
         self.freqs = rotary_frequencies(self.rotary_dim, float(p["theta"]), self.scaling)

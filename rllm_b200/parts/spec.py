@@ -75,9 +75,10 @@ class TensorSpec:
 class LayerSpec:
     block: str                       # arrangement kind, e.g. "pre_norm"
     mixer: PartSpec
-    ffn: PartSpec
+    ffn: Optional[PartSpec]          # None: the layer has no feed-forward (arrangements that allow it)
     norms: Tuple[PartSpec, ...]      # in the order the arrangement uses them
     prefix: str                      # tensor-name prefix, e.g. "model.layers.3."
+    block_params: Optional[PartSpec] = None   # sizes, constants and tensor names of the arrangement itself
 
 
 @dataclass(frozen=True)
@@ -115,11 +116,21 @@ class ModelSpec:
 @dataclass(frozen=True)
 class KVPagesNeed:
     """Keys and values of every token (``window`` None) or of the last
-    ``window`` tokens, in pages."""
+    ``window`` tokens, in pages.  ``values`` False: a token keeps ONE row of
+    ``head_dim`` values per kv head that serves as key and as value (a latent);
+    the storage then has no second buffer."""
 
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    values: bool = True
+
+    def widened(self, other: "KVPagesNeed") -> Optional["KVPagesNeed"]:
+        """The need that keeps what both keep, if the rows are the same and only the windows differ."""
+        if (self.num_kv_heads, self.head_dim, self.values) != (other.num_kv_heads, other.head_dim, other.values):
+            return None
+        w = None if self.window is None or other.window is None else max(self.window, other.window)
+        return KVPagesNeed(self.num_kv_heads, self.head_dim, w, self.values)
 
 
 @dataclass(frozen=True)
