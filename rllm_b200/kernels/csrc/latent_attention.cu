@@ -13,6 +13,7 @@
 // CUDA cores (float32 and bfloat16 rows; scores, softmax and sums in float32).
 // Rotation pairs dimension 2i with 2i+1; angles are position * f_i in float64.
 #include "tile_gemm.cuh"
+#include "tile_gemm_mma.cuh"
 #include <math.h>
 
 // ---------------------------------------------------------------------------
@@ -171,6 +172,33 @@ head_gemm_kernel(const T* __restrict__ A, long long lda, long long a_head, const
   }
 }
 
+template <int BM>
+__global__ void __launch_bounds__(TGM_THREADS)
+head_gemm_mma_kernel(const bf16* __restrict__ A, long long lda, long long a_head, const bf16* __restrict__ B,
+                     long long ldb, long long b_head, bf16* __restrict__ C, long long ldc, long long c_head, int M,
+                     int N, int K) {
+  __shared__ __align__(16) MmaTileSmem<BM, 1> sm;
+  const int h = blockIdx.z, m0 = blockIdx.y * BM, n0 = blockIdx.x * TGM_BN;
+  if (threadIdx.x < BM) {
+    const int m = m0 + threadIdx.x;
+    sm.rows[threadIdx.x] = (m < M) ? (const void*)(A + (size_t)m * lda + (size_t)h * a_head) : nullptr;
+  }
+  __syncthreads();
+  float acc[1][TgmShape<BM>::NT][4];
+  const bf16* const Bh[1] = {B + (size_t)h * b_head};
+  tile_gemm_mma<BM, 1>(sm, Bh, ldb, n0, N, K, acc);
+  int row0, col0;
+  tgm_origin<BM>(row0, col0);
+  const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+#pragma unroll
+  for (int nt = 0; nt < TgmShape<BM>::NT; ++nt)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int m = m0 + row0 + g + 8 * (i >> 1), n = n0 + col0 + nt * 8 + 2 * t + (i & 1);
+      if (m < M && n < N) C[(size_t)m * ldc + (size_t)h * c_head + n] = __float2bfloat16_rn(acc[0][nt][i]);
+    }
+}
+
 RLLM_EXPORT int rllm_head_gemm(const void* A, long long lda, long long a_head, const void* B, long long ldb,
                                long long b_head, int b_kn, void* C, long long ldc, long long c_head, int M, int N,
                                int K, int heads, int dtype, cudaStream_t stream) {
@@ -180,6 +208,17 @@ RLLM_EXPORT int rllm_head_gemm(const void* A, long long lda, long long a_head, c
   const int bm = small ? 16 : 64;
   dim3 grid((N + TG_BN - 1) / TG_BN, (M + bm - 1) / bm, heads);
   if (grid.y > 65535) return RLLM_E_UNSUPPORTED;
+  if (dtype == RLLM_DT_BF16 && !b_kn && !tgm_disabled() && K % 8 == 0 && lda % 8 == 0 && a_head % 8 == 0 &&
+      ldb % 8 == 0 && b_head % 8 == 0 && (((uintptr_t)A | (uintptr_t)B) & 15) == 0) {
+    if (small)
+      head_gemm_mma_kernel<16><<<grid, TGM_THREADS, 0, stream>>>((const bf16*)A, lda, a_head, (const bf16*)B, ldb,
+                                                                 b_head, (bf16*)C, ldc, c_head, M, N, K);
+    else
+      head_gemm_mma_kernel<64><<<grid, TGM_THREADS, 0, stream>>>((const bf16*)A, lda, a_head, (const bf16*)B, ldb,
+                                                                 b_head, (bf16*)C, ldc, c_head, M, N, K);
+    RLLM_LAUNCH_CHECK();
+    return 0;
+  }
 #define HG_LAUNCH(T_, BM_, KN_)                                                                          \
   head_gemm_kernel<T_, BM_, KN_><<<grid, TG_THREADS, 0, stream>>>((const T_*)A, lda, a_head, (const T_*)B, \
       ldb, b_head, (T_*)C, ldc, c_head, M, N, K)

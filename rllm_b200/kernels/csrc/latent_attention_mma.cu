@@ -1,0 +1,295 @@
+// Attention over cached latent rows on the tensor cores (bfloat16 rows, float32
+// scores, softmax and sums): the kernel of prompt portions and of decoding alike.
+//
+// All heads of a token read the same rows, so a CTA takes ROWS = 16 * MT consecutive
+// (token, head) pairs of ONE sequence as the rows of its tiles, and walks the keys in
+// tiles of 32 aligned to absolute positions (the arithmetic of a row does not depend
+// on the cut of the sequence, the batch or the pages).  Per key tile: the 32 cached
+// rows come in by cp.async through the block table (double buffered); warp w
+// computes the scores of keys 8w .. 8w+7 for all rows (Q . K^T, mma.sync m16n8k16);
+// the running max and sum of a row are combined across the warps in shared memory;
+// the weights are written to shared memory as bfloat16 and each warp adds P . V for
+// its own quarter of the value columns, V being the first dv columns of the very rows
+// that served as keys (ldmatrix.trans).  A sink starts a row's running max at
+// sink[h] and its sum at 1.  Exponentials are base 2 with log2(e) folded into the scale.
+#include "common.cuh"
+#include <math.h>
+
+#define LAM_THREADS 128
+#define LAM_KEYS 32
+
+__device__ __forceinline__ void lam_cp16(void* smem_dst, const void* src, bool valid) {
+  const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
+  const int n = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void lam_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <int MT, int NVT>
+__global__ void __launch_bounds__(LAM_THREADS)
+latent_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const bf16* __restrict__ cache,
+                            const int* __restrict__ block_table, int max_blocks, const int* __restrict__ q_start,
+                            const int* __restrict__ seq_lens, int heads, int dk, int dv, int ld, int page_size,
+                            int num_pages, int window, float scale_log2, const float* __restrict__ sink,
+                            int* __restrict__ err) {
+  constexpr int ROWS = 16 * MT;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* Qs = (bf16*)smem_raw;                               // [ROWS][ld]
+  bf16* Ks = Qs + (size_t)ROWS * ld;                        // [2][LAM_KEYS][ld]
+  bf16* Ps = Ks + (size_t)2 * LAM_KEYS * ld;                // [ROWS][LAM_KEYS + 8]
+  float* wmax = (float*)(Ps + ROWS * (LAM_KEYS + 8));       // [2][4][ROWS]
+  float* wsum = wmax + 2 * 4 * ROWS;                        // [2][4][ROWS]
+  float* m_cur = wsum + 2 * 4 * ROWS;                       // [ROWS]
+  float* l_cur = m_cur + ROWS;                              // [ROWS]
+
+  const int s = blockIdx.y;
+  const int t0 = q_start[s], nq = q_start[s + 1] - t0;
+  const int row_base = blockIdx.x * ROWS;                   // among the sequence's nq * heads rows
+  if (row_base >= nq * heads) return;
+  const int seq_len = seq_lens[s];
+  const int pos0 = seq_len - nq;                            // position of the sequence's first token of this step
+  const int rows_here = min(ROWS, nq * heads - row_base);
+  const int tok_lo = row_base / heads, tok_hi = (row_base + rows_here - 1) / heads;
+  const int p_lo = pos0 + tok_lo, p_hi = pos0 + tok_hi;
+  const int k_lo = (window > 0 && p_lo - window + 1 > 0) ? p_lo - window + 1 : 0;
+  const int tile_lo = k_lo / LAM_KEYS, tile_hi = p_hi / LAM_KEYS;     // inclusive
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+  const int chunks = ld / 8 - 1;                            // 16-byte chunks of a row that are loaded (the pad is not)
+  const int* bt = block_table + (size_t)s * max_blocks;
+
+  // queries: rows row_base .. of the sequence's (token, head) pairs lie one behind the other in q
+  const bf16* qsrc = q + ((size_t)t0 * heads + row_base) * dk;
+  for (int c = tid; c < ROWS * chunks; c += LAM_THREADS) {
+    const int r = c / chunks, kc = (c - r * chunks) * 8;
+    const bool ok = r < rows_here && kc < dk;
+    lam_cp16(Qs + (size_t)r * ld + kc, ok ? (const void*)(qsrc + (size_t)r * dk + kc) : (const void*)q, ok);
+  }
+  if (tid < ROWS) {
+    const int h = (row_base + tid) % heads;
+    m_cur[tid] = sink ? sink[h] * 1.4426950408889634f : -INFINITY;
+    l_cur[tid] = sink ? 1.f : 0.f;
+  }
+
+  auto load_keys = [&](int tile, int st) {
+    const int j0 = tile * LAM_KEYS;
+    bf16* dst = Ks + (size_t)st * LAM_KEYS * ld;
+    for (int c = tid; c < LAM_KEYS * chunks; c += LAM_THREADS) {
+      const int r = c / chunks, kc = (c - r * chunks) * 8;
+      const int j = j0 + r;
+      bool ok = j >= k_lo && j <= p_hi && kc < dk;
+      const bf16* src = cache;
+      if (ok) {
+        const int page = bt[j / page_size];
+        if (page < 0 || page >= num_pages) {
+          if (kc == 0) atomicOr(err, 4);
+          ok = false;
+        } else {
+          src = cache + ((size_t)page * page_size + (j % page_size)) * dk + kc;
+        }
+      }
+      lam_cp16(dst + (size_t)r * ld + kc, src, ok);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+
+  float o[MT][NVT][4];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int nt = 0; nt < NVT; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) o[mt][nt][i] = 0.f;
+  // position of each row this thread holds scores of: rows mt * 16 + g and + 8
+  int rpos[MT][2];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      const int r = mt * 16 + g + 8 * hf;
+      rpos[mt][hf] = (r < rows_here) ? pos0 + (row_base + r) / heads : -1;
+    }
+
+  load_keys(tile_lo, 0);
+  const int ksteps = (dk + 15) / 16;
+  for (int tile = tile_lo; tile <= tile_hi; ++tile) {
+    const int st = (tile - tile_lo) & 1, par = st;
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    if (tile < tile_hi) load_keys(tile + 1, st ^ 1);
+    const bf16* K = Ks + (size_t)st * LAM_KEYS * ld;
+    // ---- scores of keys 8 warp .. 8 warp + 7 for all rows
+    float sc[MT][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) sc[mt][i] = 0.f;
+    const bf16* kr = K + (size_t)(warp * 8 + g) * ld + 2 * t;
+    for (int ks = 0; ks < ksteps; ++ks) {
+      const uint32_t b0 = *(const uint32_t*)(kr + ks * 16), b1 = *(const uint32_t*)(kr + ks * 16 + 8);
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        const bf16* qr = Qs + (size_t)(mt * 16 + g) * ld + ks * 16 + 2 * t;
+        uint32_t a[4];
+        a[0] = *(const uint32_t*)qr;
+        a[1] = *(const uint32_t*)(qr + 8 * ld);
+        a[2] = *(const uint32_t*)(qr + 8);
+        a[3] = *(const uint32_t*)(qr + 8 * ld + 8);
+        lam_mma(sc[mt], a, b0, b1);
+      }
+    }
+    const int jbase = tile * LAM_KEYS + warp * 8 + 2 * t;
+    float* wm = wmax + (size_t)par * 4 * ROWS;
+    float* ws = wsum + (size_t)par * 4 * ROWS;
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        const int p = rpos[mt][hf];
+        float mx = -INFINITY;
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int j = jbase + e;
+          const bool vis = p >= 0 && j <= p && (window <= 0 || p - j < window);
+          const float v = vis ? sc[mt][2 * hf + e] * scale_log2 : -INFINITY;
+          sc[mt][2 * hf + e] = v;
+          mx = fmaxf(mx, v);
+        }
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        if (t == 0) wm[warp * ROWS + mt * 16 + g + 8 * hf] = mx;
+      }
+    __syncthreads();
+    // ---- weights, their sums, and the factor that the rows' old sums shrink by
+    float corr[MT][2];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        const int r = mt * 16 + g + 8 * hf;
+        const float mo = m_cur[r];
+        const float mn = fmaxf(fmaxf(mo, fmaxf(wm[r], wm[ROWS + r])), fmaxf(wm[2 * ROWS + r], wm[3 * ROWS + r]));
+        corr[mt][hf] = (mn == -INFINITY) ? 1.f : exp2f(mo - mn);
+        float p0 = 0.f, p1 = 0.f;
+        if (mn != -INFINITY) {
+          p0 = exp2f(sc[mt][2 * hf] - mn);
+          p1 = exp2f(sc[mt][2 * hf + 1] - mn);
+        }
+        float sum = p0 + p1;
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        if (t == 0) ws[warp * ROWS + r] = sum;
+        *(__nv_bfloat162*)(Ps + (size_t)r * (LAM_KEYS + 8) + warp * 8 + 2 * t) = __floats2bfloat162_rn(p0, p1);
+      }
+    __syncthreads();
+    if (tid < ROWS) {
+      const int r = tid;
+      const float mo = m_cur[r];
+      const float mn = fmaxf(fmaxf(mo, fmaxf(wm[r], wm[ROWS + r])), fmaxf(wm[2 * ROWS + r], wm[3 * ROWS + r]));
+      if (mn != -INFINITY) {
+        l_cur[r] = l_cur[r] * exp2f(mo - mn) + ((ws[r] + ws[ROWS + r]) + (ws[2 * ROWS + r] + ws[3 * ROWS + r]));
+        m_cur[r] = mn;
+      }
+    }
+    // ---- O = O * corr + P . V for value columns [warp * NVT * 8, (warp + 1) * NVT * 8)
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int nt = 0; nt < NVT; ++nt) {
+        o[mt][nt][0] *= corr[mt][0]; o[mt][nt][1] *= corr[mt][0];
+        o[mt][nt][2] *= corr[mt][1]; o[mt][nt][3] *= corr[mt][1];
+      }
+#pragma unroll
+    for (int kk = 0; kk < LAM_KEYS; kk += 16) {
+      uint32_t a[MT][4];
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        const bf16* pr = Ps + (size_t)(mt * 16 + g) * (LAM_KEYS + 8) + kk + 2 * t;
+        a[mt][0] = *(const uint32_t*)pr;
+        a[mt][1] = *(const uint32_t*)(pr + 8 * (LAM_KEYS + 8));
+        a[mt][2] = *(const uint32_t*)(pr + 8);
+        a[mt][3] = *(const uint32_t*)(pr + 8 * (LAM_KEYS + 8) + 8);
+      }
+#pragma unroll
+      for (int nt = 0; nt < NVT; ++nt) {
+        // V^T fragment: keys kk .. kk+15 (rows of K), columns col .. col+7; lanes 0-15 give the row addresses
+        const int col = (warp * NVT + nt) * 8;
+        const unsigned addr = (unsigned)__cvta_generic_to_shared(K + (size_t)(kk + (lane & 15)) * ld + col);
+        uint32_t b0, b1;
+        asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(b0), "=r"(b1) : "r"(addr));
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) lam_mma(o[mt][nt], a[mt], b0, b1);
+      }
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      const int r = mt * 16 + g + 8 * hf;
+      if (r >= rows_here) continue;
+      const float l = l_cur[r];
+      const float inv = l > 0.f ? 1.0f / l : 0.f;
+      bf16* orow = out + ((size_t)t0 * heads + row_base + r) * dv;
+#pragma unroll
+      for (int nt = 0; nt < NVT; ++nt) {
+        const int col = (warp * NVT + nt) * 8 + 2 * t;
+        if (col + 1 < dv) {
+          *(__nv_bfloat162*)(orow + col) = __floats2bfloat162_rn(o[mt][nt][2 * hf] * inv, o[mt][nt][2 * hf + 1] * inv);
+        } else if (col < dv) {
+          orow[col] = __float2bfloat16_rn(o[mt][nt][2 * hf] * inv);
+        }
+      }
+    }
+}
+
+template <int MT, int NVT>
+static int lam_launch(const bf16* q, bf16* out, const bf16* cache, const int* block_table, int max_blocks,
+                      const int* q_start, const int* seq_lens, int S, int max_q, int heads, int dk, int dv,
+                      int page_size, int num_pages, int window, float scale, const float* sink, int* err,
+                      cudaStream_t stream) {
+  constexpr int ROWS = 16 * MT;
+  const int dkp = (dk + 15) / 16 * 16;
+  const int ld = max(dkp, 32 * NVT) + 8;
+  const size_t smem = ((size_t)ROWS * ld + 2 * LAM_KEYS * ld + ROWS * (LAM_KEYS + 8)) * sizeof(bf16) +
+                      (size_t)(2 * 4 * ROWS * 2 + 2 * ROWS) * sizeof(float);
+  if (smem > 220 * 1024) return RLLM_E_UNSUPPORTED;
+  if (smem > 48 * 1024)
+    cudaFuncSetAttribute(latent_attention_mma_kernel<MT, NVT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  const long long blocks_x = ((long long)max_q * heads + ROWS - 1) / ROWS;
+  if (blocks_x > 2147483647LL || S > 65535) return RLLM_E_UNSUPPORTED;
+  dim3 grid((unsigned)blocks_x, S);
+  latent_attention_mma_kernel<MT, NVT><<<grid, LAM_THREADS, smem, stream>>>(
+      q, out, cache, block_table, max_blocks, q_start, seq_lens, heads, dk, dv, ld, page_size, num_pages, window,
+      scale * 1.4426950408889634f, sink, err);
+  RLLM_LAUNCH_CHECK();
+  return 0;
+}
+
+// q [T, heads * dk], out [T, heads * dv], cache [pages, 1, page_size, dk]; sequence s owns tokens
+// q_start[s] .. q_start[s+1] and holds seq_lens[s] tokens after this step; max_q: the most tokens a
+// sequence brings.  Needs dk % 8 == 0, dv <= min(dk, 512) and 16-byte aligned buffers.
+RLLM_EXPORT int rllm_latent_attention_mma(const void* q, void* out, const void* cache, const int* block_table,
+                                          int max_blocks, const int* q_start, const int* seq_lens, int S, int max_q,
+                                          int heads, int dk, int dv, int page_size, int num_pages, int window,
+                                          float scale, const float* sink, int* err, cudaStream_t stream) {
+  if (S <= 0 || max_q <= 0) return 0;
+  if (heads <= 0 || dk <= 0 || dv <= 0 || dv > dk || page_size <= 0 || num_pages <= 0 || max_blocks <= 0 ||
+      window < 0)
+    return RLLM_E_BADARG;
+  if (dk % 8 != 0 || dv > 512 || (((uintptr_t)q | (uintptr_t)out | (uintptr_t)cache) & 15) != 0)
+    return RLLM_E_UNSUPPORTED;
+#define LAM_GO(MT_, NVT_)                                                                                   \
+  return lam_launch<MT_, NVT_>((const bf16*)q, (bf16*)out, (const bf16*)cache, block_table, max_blocks, q_start, \
+                               seq_lens, S, max_q, heads, dk, dv, page_size, num_pages, window, scale, sink, err, stream)
+  if (dv <= 32) LAM_GO(4, 1);
+  if (dv <= 64) LAM_GO(4, 2);
+  if (dv <= 128) LAM_GO(4, 4);
+  if (dv <= 256) LAM_GO(4, 8);
+  LAM_GO(2, 16);
+#undef LAM_GO
+}

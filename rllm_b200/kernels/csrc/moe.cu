@@ -13,6 +13,7 @@
 // A pair's result depends on its token and its expert only: not on the rows beside
 // it in a tile, not on the order of the pairs.
 #include "tile_gemm.cuh"
+#include "tile_gemm_mma.cuh"
 #include <math.h>
 
 #define ROUTE_WARPS 4
@@ -197,6 +198,73 @@ moe_down_kernel(const T* __restrict__ y, const T* __restrict__ w, T* __restrict_
   }
 }
 
+// the same two kernels on the tensor cores (bfloat16)
+template <int BM>
+__global__ void __launch_bounds__(TGM_THREADS)
+moe_gate_up_mma_kernel(const bf16* __restrict__ h, const bf16* __restrict__ w, bf16* __restrict__ y,
+                       const int* __restrict__ offsets, const int* __restrict__ sorted,
+                       const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
+                       const int* __restrict__ meta, int H, int F, int top, float limit, float alpha) {
+  __shared__ __align__(16) MmaTileSmem<BM, 2> sm;
+  const int tile = blockIdx.y;
+  if (tile >= meta[0]) return;
+  const int e = tile_expert[tile], r0 = tile_row0[tile], rend = offsets[e + 1];
+  const int n0 = blockIdx.x * TGM_BN;
+  if (threadIdx.x < BM) {
+    const int r = r0 + threadIdx.x;
+    sm.rows[threadIdx.x] = (r < rend) ? (const void*)(h + (size_t)(sorted[r] / top) * H) : nullptr;
+  }
+  __syncthreads();
+  float acc[2][TgmShape<BM>::NT][4];
+  const bf16* we = w + (size_t)e * 2 * F * H;
+  const bf16* const B[2] = {we, we + (size_t)F * H};
+  tile_gemm_mma<BM, 2>(sm, B, H, n0, F, H, acc);
+  int row0, col0;
+  tgm_origin<BM>(row0, col0);
+  const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+#pragma unroll
+  for (int nt = 0; nt < TgmShape<BM>::NT; ++nt)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = r0 + row0 + g + 8 * (i >> 1), n = n0 + col0 + nt * 8 + 2 * t + (i & 1);
+      if (r >= rend || n >= F) continue;
+      const float gg = fminf(acc[0][nt][i], limit), uu = fminf(fmaxf(acc[1][nt][i], -limit), limit);
+      y[(size_t)r * F + n] = __float2bfloat16_rn(gg * (1.0f / (1.0f + expf(-alpha * gg))) * (uu + 1.0f));
+    }
+}
+
+template <int BM>
+__global__ void __launch_bounds__(TGM_THREADS)
+moe_down_mma_kernel(const bf16* __restrict__ y, const bf16* __restrict__ w, bf16* __restrict__ out,
+                    const int* __restrict__ offsets, const int* __restrict__ sorted,
+                    const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
+                    const int* __restrict__ meta, int H, int F) {
+  __shared__ __align__(16) MmaTileSmem<BM, 1> sm;
+  const int tile = blockIdx.y;
+  if (tile >= meta[0]) return;
+  const int e = tile_expert[tile], r0 = tile_row0[tile], rend = offsets[e + 1];
+  const int n0 = blockIdx.x * TGM_BN;
+  if (threadIdx.x < BM) {
+    const int r = r0 + threadIdx.x;
+    sm.rows[threadIdx.x] = (r < rend) ? (const void*)(y + (size_t)r * F) : nullptr;
+  }
+  __syncthreads();
+  float acc[1][TgmShape<BM>::NT][4];
+  const bf16* const B[1] = {w + (size_t)e * H * F};
+  tile_gemm_mma<BM, 1>(sm, B, F, n0, H, F, acc);
+  int row0, col0;
+  tgm_origin<BM>(row0, col0);
+  const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+#pragma unroll
+  for (int nt = 0; nt < TgmShape<BM>::NT; ++nt)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = r0 + row0 + g + 8 * (i >> 1), n = n0 + col0 + nt * 8 + 2 * t + (i & 1);
+      if (r >= rend || n >= H) continue;
+      out[(size_t)sorted[r] * H + n] = __float2bfloat16_rn(acc[0][nt][i]);
+    }
+}
+
 // out[t, :] = sum_k c[t, k] y[t * K + k, :], the k terms in order
 template <typename T>
 __global__ void weighted_slot_sum_kernel(const T* __restrict__ y, const float* __restrict__ c, T* __restrict__ out,
@@ -230,6 +298,21 @@ RLLM_EXPORT int rllm_moe_experts(const void* h, const void* w_gate_up, const voi
   if (H <= 0 || F <= 0 || top <= 0 || (bm != 16 && bm != 64)) return RLLM_E_BADARG;
   if (max_tiles > 65535) return RLLM_E_UNSUPPORTED;
   dim3 g1((F + TG_BN - 1) / TG_BN, max_tiles), g2((H + TG_BN - 1) / TG_BN, max_tiles);
+  const bool aligned = H % 8 == 0 && F % 8 == 0 &&
+                       (((uintptr_t)h | (uintptr_t)w_gate_up | (uintptr_t)w_down | (uintptr_t)y) & 15) == 0;
+  if (dtype == RLLM_DT_BF16 && aligned && !tgm_disabled()) {
+#define MOE_MMA(BM_)                                                                                         \
+  do {                                                                                                       \
+    moe_gate_up_mma_kernel<BM_><<<g1, TGM_THREADS, 0, stream>>>((const bf16*)h, (const bf16*)w_gate_up,      \
+        (bf16*)y, offsets, sorted, tile_expert, tile_row0, meta, H, F, top, limit, alpha);                   \
+    moe_down_mma_kernel<BM_><<<g2, TGM_THREADS, 0, stream>>>((const bf16*)y, (const bf16*)w_down, (bf16*)out, \
+        offsets, sorted, tile_expert, tile_row0, meta, H, F);                                                \
+  } while (0)
+    if (bm == 16) MOE_MMA(16); else MOE_MMA(64);
+#undef MOE_MMA
+    RLLM_LAUNCH_CHECK();
+    return 0;
+  }
 #define MOE_LAUNCH(T_, BM_)                                                                                  \
   do {                                                                                                       \
     moe_gate_up_kernel<T_, BM_><<<g1, TG_THREADS, 0, stream>>>((const T_*)h, (const T_*)w_gate_up, (T_*)y,    \

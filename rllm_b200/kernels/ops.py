@@ -780,6 +780,34 @@ def latent_attention_simt(q: torch.Tensor, out: torch.Tensor, cache: torch.Tenso
            "latent_attention_simt")
 
 
+def latent_attention_mma_takes(dtype: torch.dtype, dk: int, dv: int) -> bool:
+    """Whether the tensor-core kernel computes this attention (RLLM_LATENT_ATTENTION=simt keeps it on the CUDA cores)."""
+    import os
+    return (dtype is torch.bfloat16 and dk % 8 == 0 and dv <= min(dk, 512)
+            and os.environ.get("RLLM_LATENT_ATTENTION") != "simt")
+
+
+def latent_attention_mma(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
+                         q_start: torch.Tensor, seq_lens: torch.Tensor, num_seqs: int, max_q_len: int, heads: int,
+                         dk: int, dv: int, window: int, scale: float, sink: Optional[torch.Tensor],
+                         err: torch.Tensor) -> None:
+    """The same attention as ``latent_attention_simt`` on the tensor cores, for bfloat16.  Sequence s owns
+    tokens q_start[s] .. q_start[s+1], the last of them at position seq_lens[s] - 1; ``max_q_len``: the most
+    tokens a sequence brings (sizes the grid)."""
+    lib = build.load_library("latent_attention_mma")
+    T = q.shape[0]
+    assert q.shape == (T, heads * dk) and out.shape == (T, heads * dv) and cache.shape[3] == dk
+    assert q.dtype is torch.bfloat16 and cache.dtype is torch.bfloat16 and out.dtype is torch.bfloat16
+    _contig(q, "q"); _contig(out, "out"); _contig(cache, "cache"); _contig(block_table, "block_table")
+    if sink is not None:
+        assert sink.dtype is torch.float32 and sink.numel() == heads
+    _check(lib.rllm_latent_attention_mma(_ptr(q), _ptr(out), _ptr(cache), _ptr(block_table),
+                                         c_int(block_table.shape[1]), _ptr(q_start), _ptr(seq_lens), c_int(num_seqs),
+                                         c_int(max_q_len), c_int(heads), c_int(dk), c_int(dv), c_int(cache.shape[2]),
+                                         c_int(cache.shape[0]), c_int(window), c_float(scale), _ptr(sink), _ptr(err),
+                                         _stream()), "latent_attention_mma")
+
+
 # ---------------------------------------------------------------------------
 # routed experts (moe.cu)
 # ---------------------------------------------------------------------------

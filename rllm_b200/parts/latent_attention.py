@@ -96,7 +96,8 @@ class LatentAttention(Mixer):
             self.w_kvn = tensors[n["dkv_norm"]].contiguous()
         self.w_qn = tensors[n["dq_norm"]].contiguous()
         self.w_uq = tensors[n["uq"]]
-        self.w_uk = tensors[n["uk"]].contiguous().view(H, self.nope, self.kv_rank)      # [h, k = nope, n = kv_rank]
+        # W_uk[h]^T, [h, n = kv_rank, k = nope]: the query-side product reads it along k
+        self.w_uk = tensors[n["uk"]].view(H, self.nope, self.kv_rank).transpose(1, 2).contiguous()
         self.w_uv = tensors[n["uv"]].contiguous().view(H, self.vdim, self.kv_rank)      # [h, n = vdim, k = kv_rank]
         self.w_o = tensors[n["o"]]
         self.sink = tensors[n["sink"]].float().contiguous() if self.has_sink else None
@@ -117,12 +118,16 @@ class LatentAttention(Mixer):
         q = linear(cq, self.w_uq)                                    # [T, H (nope + rot)]
         qt = torch.empty((T, H * dk), dtype=x.dtype, device=x.device)
         ops.head_gemm(q.view(T, H, self.nope + self.rot)[:, :, : self.nope], self.w_uk,
-                      qt.view(T, H, dk)[:, :, : self.kv_rank], b_kn=True)
+                      qt.view(T, H, dk)[:, :, : self.kv_rank], b_kn=False)
         if self.rot:
             ops.latent_q_rot(q, qt, ctx.positions, inv_freq, H, self.nope, self.rot, self.rot_dims, self.kv_rank)
         o = torch.empty((T, H * self.kv_rank), dtype=x.dtype, device=x.device)
-        ops.latent_attention_simt(qt, o, cache.k, table, ctx.positions, ctx.token_seq, H, dk, self.kv_rank,
-                                  int(self.window or 0), self.scale, self.sink, ctx.err)
+        if ops.latent_attention_mma_takes(x.dtype, dk, self.kv_rank):
+            ops.latent_attention_mma(qt, o, cache.k, table, ctx.q_start, ctx.seq_lens, ctx.num_seqs, ctx.max_q_len, H,
+                                     dk, self.kv_rank, int(self.window or 0), self.scale, self.sink, ctx.err)
+        else:
+            ops.latent_attention_simt(qt, o, cache.k, table, ctx.positions, ctx.token_seq, H, dk, self.kv_rank,
+                                      int(self.window or 0), self.scale, self.sink, ctx.err)
         ov = torch.empty((T, H * self.vdim), dtype=x.dtype, device=x.device)
         ops.head_gemm(o.view(T, H, self.kv_rank), self.w_uv, ov.view(T, H, self.vdim), b_kn=False)
         return linear(ov, self.w_o)

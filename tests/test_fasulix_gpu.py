@@ -108,6 +108,57 @@ def test_latent_attention_over_paged_rows(dtype, window, sink, dk, dv, page):
     assert rel(got, want) <= (3e-6 if dtype == "float32" else 2e-2)
 
 
+@pytest.mark.parametrize("window,sink,dk,dv,page,heads", [(0, True, 56, 48, 16, 3), (7, False, 24, 8, 4, 5), (33, False, 144, 128, 8, 6),
+                                                           (1, False, 40, 40, 16, 1), (0, False, 304, 260, 16, 2),
+                                                           (40, True, 576, 512, 16, 16), (0, False, 96, 64, 32, 20)])
+def test_latent_attention_on_the_tensor_cores(window, sink, dk, dv, page, heads):
+    """Three sequences in one launch: a prompt portion that continues a cached prefix, a single decoded
+    token, and a whole short prompt; rows on shuffled pages; against the formula in float64."""
+    from rllm_b200.kernels import ops
+    g = torch.Generator().manual_seed(dk + window)
+    lens, news = [83, 41, 19], [50, 1, 19]
+    T = sum(news)
+    n_pages = sum(-(-n // page) for n in lens)
+    perm = torch.randperm(n_pages + 2, generator=g)
+    cache = torch.zeros(n_pages + 2, 1, page, dk, dtype=torch.bfloat16)
+    width = max(-(-n // page) for n in lens)
+    table = torch.full((3, width), -1, dtype=torch.int32)
+    rows, used = [], 0
+    for s, n in enumerate(lens):
+        r = torch.randn(n, dk, generator=g).to(torch.bfloat16)
+        rows.append(r)
+        for j in range(n):
+            if j % page == 0:
+                table[s, j // page] = perm[used]
+                used += 1
+            cache[table[s, j // page], 0, j % page] = r[j]
+    q = torch.randn(T, heads, dk, generator=g).to(torch.bfloat16)
+    sk = (torch.randn(heads, generator=g) + 1.0) if sink else None
+    scale = dk ** -0.5
+    out = torch.empty(T, heads * dv, dtype=torch.bfloat16, device="cuda")
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    q_start = torch.tensor([0, 50, 51, 70], dtype=torch.int32, device="cuda")
+    ops.latent_attention_mma(q.reshape(T, heads * dk).cuda(), out, cache.cuda(), table.cuda(), q_start,
+                             torch.tensor(lens, dtype=torch.int32, device="cuda"), 3, max(news), heads, dk, dv, window,
+                             scale, sk.cuda() if sink else None, err)
+    assert int(err.item()) == 0
+    want = torch.zeros(T, heads, dv, dtype=torch.float64)
+    off = 0
+    for s, (n, m) in enumerate(zip(lens, news)):
+        rd = rows[s].double()
+        for i in range(m):
+            p = n - m + i
+            lo = max(0, p - window + 1) if window else 0
+            for h in range(heads):
+                sc = rd[lo:p + 1] @ q[off + i, h].double() * scale
+                top = max(float(sc.max()), float(sk[h])) if sink else float(sc.max())
+                e = torch.exp(sc - top)
+                den = e.sum() + (math.exp(float(sk[h]) - top) if sink else 0.0)
+                want[off + i, h] = (e / den) @ rd[lo:p + 1, :dv]
+        off += m
+    assert rel(out.view(T, heads, dv), want) <= 2e-2
+
+
 @pytest.mark.parametrize("window", [5, 16, 17])
 def test_a_key_just_inside_and_just_outside_the_window_and_a_far_key(window):
     """Row 3 and the query of the last token are scaled so that row 3's score stands far out.  A query sees
@@ -280,6 +331,18 @@ def compare(got, want, reqs, dtype, what):
 def make_requests(vocab, lengths, seed):
     rng = np.random.default_rng(seed)
     return {f"r{i}": [int(t) for t in rng.integers(0, vocab, size=n)] for i, n in enumerate(lengths)}
+
+
+def test_the_cuda_core_forms_of_the_bfloat16_kernels_still_serve(fx_dirs, monkeypatch):
+    """RLLM_LATENT_ATTENTION=simt and RLLM_TILE_GEMM=simt (read once per process by the library, so set before its
+    first call in a child process) keep attention and the tile products off the tensor cores."""
+    V = FX_B["vocab"]
+    reqs = make_requests(V, [40, 9], seed=21)
+    want = plain_rows(fx_dirs["B"], "bfloat16", reqs)
+    monkeypatch.setenv("RLLM_LATENT_ATTENTION", "simt")
+    monkeypatch.setenv("RLLM_TILE_GEMM", "simt")
+    got = ru.run_trace(fx_dirs["B"], "bfloat16", ru.trace_portions(reqs, seed=2), V, page_size=16, subprocess_mode=True)
+    compare(got, want, reqs, "bfloat16", "cuda-core forms")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
