@@ -392,6 +392,234 @@ def workload_8b(pk, windows):
                         enable_prefix_caching=True)
 
 
+# -- two designs side by side: Fasulix and the Llama of equal size ------------------------------------------
+def fasulix(layers, width, heads, dim, rot, vdim, q_rank, kv_rank, gru, experts, top, ff, window, vocab):
+    """layers of the pattern [latent attention with sink, minGRU, windowed latent attention, minGRU]."""
+    def latent(kind):
+        m = {"heads": heads, "dim": dim, "rot_dim": rot, "vdim": vdim, "q_rank": q_rank, "kv_rank": kv_rank,
+             "rot": {"base": 500000.0, "dims": rot}, "scale": (dim + rot) ** -0.5}
+        if kind == "latent_attention_2":
+            m["mask"] = {"size": window}
+        return m
+    mlp = {"kind": "moe", "expert": {"ff": ff, "limit": 7.0}, "router": {"experts": experts, "top": top}}
+    kinds = ["latent_attention", "mingru", "latent_attention_2", "mingru"]
+    return {"architecture": "Fasulix", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "max_positions": 8192,
+            "layers": [{"type": kinds[i % 4], "mlp": mlp,
+                        "mixer": {"width": gru} if kinds[i % 4] == "mingru" else latent(kinds[i % 4])}
+                       for i in range(layers)]}
+
+
+# (name, Fasulix sizes, the Llama beside it: same width, layers, heads and vocabulary, head size dim + rot,
+#  an intermediate size of top * ff, so that a token multiplies as many feed-forward weights)
+DESIGN_SIZES = [
+    ("w1024", dict(layers=4, width=1024, heads=8, dim=64, rot=32, vdim=64, q_rank=384, kv_rank=256, gru=1024,
+                   experts=16, top=2, ff=1024, window=512, vocab=32768),
+     dict(layers=4, hidden=1024, heads=16, kv_heads=4, head_dim=64, inter=2048)),
+    ("w2048", dict(layers=4, width=2048, heads=16, dim=128, rot=64, vdim=128, q_rank=768, kv_rank=512, gru=2048,
+                   experts=32, top=4, ff=1024, window=1024, vocab=32768),
+     dict(layers=4, hidden=2048, heads=16, kv_heads=4, head_dim=128, inter=4096)),
+]
+
+
+def compare_designs(args):
+    """Prefill and decode throughput of Fasulix at sizes that resemble a real model's layers (random weights)
+    beside the Llama of equal size, through the same step function; and, from one eager prefill step and one
+    eager decode step of each, the device time of every kernel of the step by entry point, with what the
+    kernel has to move or multiply at the least, as a fraction of the measured peaks."""
+    import numpy as np
+    import torch
+
+    from rllm_b200 import LLM
+    from rllm_b200.engine.runner import StepEntry
+    from rllm_b200.kernels import ops
+
+    pk = peaks()
+    T, B, CTX, K, W = args.prompt_len, args.batch, args.prompt_len, min(args.steps, 64), max(3, args.warmup)
+    clocks = ClockSampler()
+    clocks.start()
+    windows, rows = [], []
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+
+    def roofline(name, a, kw, shape):
+        """(flops, bytes) a call has to do at the least, from its arguments; None: not modelled."""
+        S, ctx, Tn = shape["seqs"], shape["ctx"], shape["tokens"]
+        pairs = sum(min(p + 1, shape.get("window") or p + 1) for p in range(ctx - Tn // S, ctx)) * S
+        if name == "latent_attention_mma":
+            q, heads, dk, dv, window = a[0], a[8], a[9], a[10], a[11]
+            vis = sum(min(p + 1, window or p + 1) for p in range(ctx - Tn // S, ctx)) * S
+            keys = S * min(ctx, (window or ctx) + Tn // S)
+            return 2.0 * (dk + dv) * heads * vis, 2.0 * (keys * dk + q.numel() + a[1].numel())
+        if name in ("attention_prefill_tcgen05", "attention_prefill_bf16", "attention_decode_bf16"):
+            nq, nkv, d = (a[11], a[12], a[13]) if name != "attention_decode_bf16" else (a[9], a[10], a[11])
+            return 4.0 * d * nq * pairs, 2.0 * (2 * S * ctx * nkv * d + 2 * Tn * nq * d)
+        if name == "moe_experts":
+            h, ids, wgu = a[0], a[1], a[2]
+            E, F2, H = wgu.shape
+            P = ids.numel()
+            used = min(E, P)
+            return 2.0 * 3 * H * (F2 // 2) * P, 2.0 * (used * 3 * H * (F2 // 2) + h.numel() + P * (H + F2))
+        if name == "head_gemm":
+            M, heads, Kd = a[0].shape
+            N = a[2].shape[2]
+            return 2.0 * M * heads * Kd * N, 2.0 * (a[0].numel() + a[1].numel() + M * heads * N)
+        if name == "mingru_scan":
+            return 0.0, 2.0 * (a[0].numel() + a[7].numel())
+        if name == "gated_postnorm_add":
+            return 0.0, 8.0 * a[0].numel() + 2.0 * (a[2].numel() + 2 * a[3].numel())
+        if name == "depth_average":
+            return 0.0, 4.0 * a[1] * a[0][0].numel() + 6.0 * a[0][0].numel()
+        if name == "rmsnorm":
+            return 0.0, a[3].numel() * 10.0
+        if name == "silu_mul":
+            return 0.0, a[1].numel() * 6.0
+        if name in ("latent_prep", "latent_q_rot", "moe_route", "rope_kv_write"):
+            return 0.0, 4.0 * a[0].numel()
+        if name in ("gemm_tcgen05", "gemm_small_m", "gemm_small_m_rstd", "gemm_small_m_residual"):
+            x, w = (a[0], a[1]) if name != "gemm_small_m_rstd" else (a[0], a[3])
+            rows_out = w.shape[0] // 2 if (len(a) > 3 and a[-1] == "silu_mul") else w.shape[0]
+            return 2.0 * x.shape[0] * x.shape[1] * w.shape[0], 2.0 * (x.numel() + w.numel() + x.shape[0] * rows_out)
+        return None
+
+    def kernel_table(runner, entries, shape):
+        """One eager step with CUDA events around every entry point of ``ops`` (L2 flushed before the step)."""
+        names = [n for n in dir(ops) if callable(getattr(ops, n)) and n in (
+            "latent_attention_mma", "attention_prefill_tcgen05", "attention_prefill_bf16", "attention_decode_bf16",
+            "moe_experts", "moe_route", "head_gemm", "mingru_scan", "gated_postnorm_add", "depth_average", "rmsnorm",
+            "silu_mul", "latent_prep", "latent_q_rot", "rope_kv_write", "gemm_small_m", "moe_choose", "gemm_small_m_residual",
+            "gemm_small_m_rstd", "gemm_tcgen05", "embedding")]
+        saved, log = {}, []
+
+        def wrap(name, fn):
+            def timed(*a, **kw):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                out = fn(*a, **kw)
+                e1.record()
+                log.append((name, e0, e1, roofline(name, a, kw, shape)))
+                return out
+            return timed
+        mm = torch.mm
+
+        def timed_mm(x, w, **kw):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            out = mm(x, w, **kw)
+            e1.record()
+            log.append(("library_mm", e0, e1, (2.0 * x.shape[0] * x.shape[1] * w.shape[1],
+                                               2.0 * (x.numel() + w.numel() + x.shape[0] * w.shape[1]))))
+            return out
+        for n in names:
+            saved[n] = getattr(ops, n)
+            setattr(ops, n, wrap(n, saved[n]))
+        torch.mm = timed_mm
+        was = runner.capture_graphs
+        runner.capture_graphs = False
+        try:
+            runner.step(entries)               # every kernel of the step has run once (module loading, first-call setup)
+            torch.cuda.synchronize()
+            log.clear()
+            flush.zero_()
+            runner.step(entries)
+            torch.cuda.synchronize()
+        finally:
+            runner.capture_graphs = was
+            torch.mm = mm
+            for n, f in saved.items():
+                setattr(ops, n, f)
+        agg = {}
+        for name, e0, e1, need in log:
+            ms = e0.elapsed_time(e1)
+            a = agg.setdefault(name, [0, 0.0, 0.0, 0.0])
+            a[0] += 1
+            a[1] += ms
+            if need is not None:
+                a[2] += need[0]
+                a[3] += need[1]
+        out = {}
+        for name, (n, ms, fl, by) in sorted(agg.items(), key=lambda kv: -kv[1][1]):
+            floor_ms = max(fl / (pk["bf16_tflops"] * 1e12), by / (pk["hbm_gbs"] * 1e9)) * 1e3
+            out[name] = {"calls": n, "ms": round(ms, 4), "of_roofline": round(floor_ms / ms, 3) if floor_ms else None,
+                         "bound": "compute" if fl / (pk["bf16_tflops"] * 1e12) > by / (pk["hbm_gbs"] * 1e9) else "memory"}
+        return out
+
+    def measure(label, cfg):
+        d = write_config(cfg)
+        pages = (B + 1) * (-(-(CTX + K + W + 8) // BLOCK_SIZE) + 2) + 64
+        llm = LLM(d, dtype="bf16", max_model_len=CTX + K + W + 8, max_num_seqs=B + 1, max_num_batched_tokens=8192,
+                  long_prefill_token_threshold=8192, block_size=BLOCK_SIZE, num_gpu_blocks=pages,
+                  enable_prefix_caching=False, random_weights=True, seed=0, draw_on_device=True)
+        eng, runner = llm.engine, llm.engine.runner
+        vocab = eng.model.spec.vocab_size
+        rng = np.random.default_rng(0)
+        toks = lambda n: [int(t) for t in rng.integers(0, vocab, size=n)]
+        # prefill: whole prompts of T tokens, one a step, timed on the device
+        ms_all = []
+        a = time.time()
+        for i in range(W + 5):
+            eng.cache.admit("p")
+            assert eng.cache.ensure("p", 0, T)
+            entries = [StepEntry("p", toks(T), 0, [T - 1])]
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            runner.step(entries)
+            e1.record()
+            torch.cuda.synchronize()
+            if i >= W:
+                ms_all.append(e0.elapsed_time(e1))
+            if i == W + 4:
+                eng.cache.free("p")
+                eng.cache.admit("p")
+                assert eng.cache.ensure("p", 0, T)
+                table_p = kernel_table(runner, [StepEntry("p", toks(T), 0, [T - 1])],
+                                       {"seqs": 1, "ctx": T, "tokens": T})
+            eng.cache.free("p")
+        prefill_ms = sorted(ms_all)[len(ms_all) // 2]
+        # decode: B sequences that hold CTX tokens each
+        ids = [f"d{i}" for i in range(B)]
+        for i in ids:
+            eng.cache.admit(i)
+            assert eng.cache.ensure(i, 0, CTX + K + W + 2)
+        per = max(1, 8192 // CTX)
+        for x in range(0, B, per):
+            runner.step([StepEntry(i, toks(CTX), 0, []) for i in ids[x:x + per]])
+        entries = [StepEntry(i, toks(1), CTX, [0]) for i in ids]
+        table_d = kernel_table(runner, entries, {"seqs": B, "ctx": CTX + 1, "tokens": B})
+        entries = [StepEntry(i, toks(1), CTX + 1, [0]) for i in ids]
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        runner.greedy_decode_run(entries, W + K, timing=(W, e0, e1))
+        torch.cuda.synchronize()
+        windows.append((a, time.time()))
+        decode_ms = e0.elapsed_time(e1) / K
+        runner.check_errors()
+        for i in ids:
+            eng.cache.free(i)
+        res = {"design": label, "weights_gb": round(eng.model.num_weight_bytes() / 1e9, 3),
+               "prefill_tok_s": round(T / (prefill_ms / 1e3), 1), "prefill_ms": round(prefill_ms, 3),
+               "decode_tok_s": round(B / (decode_ms / 1e3), 1), "decode_ms_per_step": round(decode_ms, 4),
+               "kernels_prefill": table_p, "kernels_decode": table_d}
+        del llm, eng, runner
+        torch.cuda.empty_cache()
+        return res
+
+    for name, fx, ll in DESIGN_SIZES:
+        if args.design_size and name != args.design_size:
+            continue
+        f = measure("fasulix", fasulix(**fx))
+        cfg = llama(ll["layers"], ll["hidden"], ll["heads"], ll["kv_heads"], ll["head_dim"], ll["inter"], 32.0, True)
+        cfg["vocab_size"] = fx["vocab"]
+        m = measure("llama", cfg)
+        rows.append({"size": name, "fasulix": f, "llama": m})
+    clocks.stop()
+    print(json.dumps({"metric": "fasulix_vs_llama_step_throughput", "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16",
+                      "data": "synthetic", "prompt_len": T, "decode_batch": B, "decode_context": CTX,
+                      "timing": "CUDA events; prefill: median of 5 steps after warm-up, 256 MiB written between steps; "
+                                "decode: %d graph steps on the device" % K,
+                      "peaks": pk, "clocks": clocks.summary(windows), "sizes": rows}))
+    return 0
+
+
 def main():
     global SETTLE_STEPS
     ap = argparse.ArgumentParser()
@@ -407,8 +635,14 @@ def main():
     ap.add_argument("--no-standin", action="store_true", help="skip the library-operator stand-in")
     ap.add_argument("--settle-steps", type=int, default=SETTLE_STEPS,
                     help="untimed decode steps of a device-timed point before its warm-up steps (0 for a short capture under a profiler)")
+    ap.add_argument("--design", default=None, choices=["fasulix"],
+                    help="instead of the default workload: this design beside the Llama of equal size (prefill and "
+                         "decode throughput, kernels against their rooflines)")
+    ap.add_argument("--design-size", default=None, help="only this entry of the design comparison's sizes")
     args = ap.parse_args()
     SETTLE_STEPS = max(0, args.settle_steps)
+    if args.design:
+        return compare_designs(args)
 
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":

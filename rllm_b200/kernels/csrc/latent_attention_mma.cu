@@ -12,6 +12,12 @@
 // its own quarter of the value columns, V being the first dv columns of the very rows
 // that served as keys (ldmatrix.trans).  A sink starts a row's running max at
 // sink[h] and its sum at 1.  Exponentials are base 2 with log2(e) folded into the scale.
+//
+// Few rows and many keys (decoding): the key tiles are also cut into splits of
+// `split_tiles` tiles at absolute tile numbers, one CTA each (grid z); a split leaves
+// its unnormalised sums, running max and sum in a work buffer and a second kernel
+// adds the splits of a row in order (and the sink).  Where the cuts fall depends on
+// the row's own sequence only.
 #include "common.cuh"
 #include <math.h>
 
@@ -35,7 +41,7 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, 
                             const int* __restrict__ block_table, int max_blocks, const int* __restrict__ q_start,
                             const int* __restrict__ seq_lens, int heads, int dk, int dv, int ld, int page_size,
                             int num_pages, int window, float scale_log2, const float* __restrict__ sink,
-                            int* __restrict__ err) {
+                            int split_tiles, float* __restrict__ work, int* __restrict__ err) {
   constexpr int ROWS = 16 * MT;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* Qs = (bf16*)smem_raw;                               // [ROWS][ld]
@@ -56,7 +62,22 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, 
   const int tok_lo = row_base / heads, tok_hi = (row_base + rows_here - 1) / heads;
   const int p_lo = pos0 + tok_lo, p_hi = pos0 + tok_hi;
   const int k_lo = (window > 0 && p_lo - window + 1 > 0) ? p_lo - window + 1 : 0;
-  const int tile_lo = k_lo / LAM_KEYS, tile_hi = p_hi / LAM_KEYS;     // inclusive
+  int tile_lo = k_lo / LAM_KEYS, tile_hi = p_hi / LAM_KEYS;           // inclusive
+  const int dvp = 32 * NVT;
+  float* wrow = nullptr;              // split mode: where this CTA's rows leave their partial results
+  if (split_tiles > 0) {
+    tile_lo = max(tile_lo, (int)blockIdx.z * split_tiles);
+    tile_hi = min(tile_hi, (int)(blockIdx.z + 1) * split_tiles - 1);
+    wrow = work + (((size_t)s * gridDim.x * ROWS + row_base) * gridDim.z + blockIdx.z) * (dvp + 2);
+    if (tile_lo > tile_hi) {          // nothing of this split is visible: an empty partial result
+      if (threadIdx.x < rows_here) {
+        float* w = wrow + (size_t)threadIdx.x * gridDim.z * (dvp + 2);
+        w[dvp] = -INFINITY;
+        w[dvp + 1] = 0.f;
+      }
+      return;
+    }
+  }
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
   const int chunks = ld / 8 - 1;                            // 16-byte chunks of a row that are loaded (the pad is not)
   const int* bt = block_table + (size_t)s * max_blocks;
@@ -70,8 +91,9 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, 
   }
   if (tid < ROWS) {
     const int h = (row_base + tid) % heads;
-    m_cur[tid] = sink ? sink[h] * 1.4426950408889634f : -INFINITY;
-    l_cur[tid] = sink ? 1.f : 0.f;
+    const bool with_sink = sink != nullptr && split_tiles <= 0;      // split mode: the merge adds the sink
+    m_cur[tid] = with_sink ? sink[h] * 1.4426950408889634f : -INFINITY;
+    l_cur[tid] = with_sink ? 1.f : 0.f;
   }
 
   auto load_keys = [&](int tile, int st) {
@@ -232,6 +254,17 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, 
     for (int hf = 0; hf < 2; ++hf) {
       const int r = mt * 16 + g + 8 * hf;
       if (r >= rows_here) continue;
+      if (wrow != nullptr) {
+        float* w = wrow + (size_t)r * gridDim.z * (dvp + 2);
+#pragma unroll
+        for (int nt = 0; nt < NVT; ++nt) {
+          const int col = (warp * NVT + nt) * 8 + 2 * t;
+          w[col] = o[mt][nt][2 * hf];
+          w[col + 1] = o[mt][nt][2 * hf + 1];
+        }
+        if (warp == 0 && t == 0) { w[dvp] = m_cur[r]; w[dvp + 1] = l_cur[r]; }
+        continue;
+      }
       const float l = l_cur[r];
       const float inv = l > 0.f ? 1.0f / l : 0.f;
       bf16* orow = out + ((size_t)t0 * heads + row_base + r) * dv;
@@ -247,11 +280,48 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, 
     }
 }
 
+// one warp per (sequence, row): the splits' partial results in order, and the sink
+__global__ void __launch_bounds__(128)
+latent_attention_merge_kernel(const float* __restrict__ work, bf16* __restrict__ out, const int* __restrict__ q_start,
+                              int heads, int dv, int dvp, int max_rows, int nsplit, const float* __restrict__ sink) {
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * 4 + (threadIdx.x >> 5), s = blockIdx.y;
+  const int t0 = q_start[s], nq = q_start[s + 1] - t0;
+  if (row >= nq * heads) return;
+  const float* w = work + (((size_t)s * max_rows + row) * nsplit) * (dvp + 2);
+  const float sk = sink ? sink[row % heads] * 1.4426950408889634f : -INFINITY;
+  float M = sk;
+  for (int z = 0; z < nsplit; ++z) M = fmaxf(M, w[(size_t)z * (dvp + 2) + dvp]);
+  float L = sink ? exp2f(sk - M) : 0.f;
+  float acc[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) acc[i] = 0.f;
+  for (int z = 0; z < nsplit; ++z) {
+    const float* p = w + (size_t)z * (dvp + 2);
+    const float m = p[dvp], l = p[dvp + 1];
+    if (l <= 0.f || m == -INFINITY) continue;
+    const float f = exp2f(m - M);
+    L = fmaf(l, f, L);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int c = lane + 32 * i;
+      if (c < dv) acc[i] = fmaf(p[c], f, acc[i]);
+    }
+  }
+  const float inv = L > 0.f ? 1.0f / L : 0.f;
+  bf16* orow = out + ((size_t)t0 * heads + row) * dv;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const int c = lane + 32 * i;
+    if (c < dv) orow[c] = __float2bfloat16_rn(acc[i] * inv);
+  }
+}
+
 template <int MT, int NVT>
 static int lam_launch(const bf16* q, bf16* out, const bf16* cache, const int* block_table, int max_blocks,
                       const int* q_start, const int* seq_lens, int S, int max_q, int heads, int dk, int dv,
-                      int page_size, int num_pages, int window, float scale, const float* sink, int* err,
-                      cudaStream_t stream) {
+                      int page_size, int num_pages, int window, float scale, const float* sink, int split_tiles,
+                      int nsplit, float* work, int* err, cudaStream_t stream) {
   constexpr int ROWS = 16 * MT;
   const int dkp = (dk + 15) / 16 * 16;
   const int ld = max(dkp, 32 * NVT) + 8;
@@ -262,12 +332,27 @@ static int lam_launch(const bf16* q, bf16* out, const bf16* cache, const int* bl
     cudaFuncSetAttribute(latent_attention_mma_kernel<MT, NVT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   const long long blocks_x = ((long long)max_q * heads + ROWS - 1) / ROWS;
   if (blocks_x > 2147483647LL || S > 65535) return RLLM_E_UNSUPPORTED;
-  dim3 grid((unsigned)blocks_x, S);
+  dim3 grid((unsigned)blocks_x, S, split_tiles > 0 ? nsplit : 1);
   latent_attention_mma_kernel<MT, NVT><<<grid, LAM_THREADS, smem, stream>>>(
       q, out, cache, block_table, max_blocks, q_start, seq_lens, heads, dk, dv, ld, page_size, num_pages, window,
-      scale * 1.4426950408889634f, sink, err);
+      scale * 1.4426950408889634f, sink, split_tiles, work, err);
   RLLM_LAUNCH_CHECK();
+  if (split_tiles > 0) {
+    const int max_rows = (int)blocks_x * ROWS;
+    dim3 mg((max_rows + 3) / 4, S);
+    latent_attention_merge_kernel<<<mg, 128, 0, stream>>>(work, out, q_start, heads, dv, 32 * NVT, max_rows, nsplit, sink);
+    RLLM_LAUNCH_CHECK();
+  }
   return 0;
+}
+
+// work size in floats for a split launch: rows are padded to the row tile the launch will choose
+RLLM_EXPORT long long rllm_latent_attention_mma_work(int S, int max_q, int heads, int dv, int nsplit) {
+  const long long rows = (long long)max_q * heads;
+  const int mt = rows <= 16 ? 1 : (rows <= 32 ? 2 : (dv > 256 ? 2 : 4));
+  const int nvt = dv <= 32 ? 1 : (dv <= 64 ? 2 : (dv <= 128 ? 4 : (dv <= 256 ? 8 : 16)));
+  const long long padded = (rows + 16 * mt - 1) / (16 * mt) * (16 * mt);
+  return (long long)S * padded * nsplit * (32 * nvt + 2);
 }
 
 // q [T, heads * dk], out [T, heads * dv], cache [pages, 1, page_size, dk]; sequence s owns tokens
@@ -276,8 +361,10 @@ static int lam_launch(const bf16* q, bf16* out, const bf16* cache, const int* bl
 RLLM_EXPORT int rllm_latent_attention_mma(const void* q, void* out, const void* cache, const int* block_table,
                                           int max_blocks, const int* q_start, const int* seq_lens, int S, int max_q,
                                           int heads, int dk, int dv, int page_size, int num_pages, int window,
-                                          float scale, const float* sink, int* err, cudaStream_t stream) {
+                                          float scale, const float* sink, int split_tiles, int nsplit, float* work,
+                                          int* err, cudaStream_t stream) {
   if (S <= 0 || max_q <= 0) return 0;
+  if (split_tiles > 0 && (nsplit <= 0 || nsplit > 65535 || work == nullptr)) return RLLM_E_BADARG;
   if (heads <= 0 || dk <= 0 || dv <= 0 || dv > dk || page_size <= 0 || num_pages <= 0 || max_blocks <= 0 ||
       window < 0)
     return RLLM_E_BADARG;
@@ -285,11 +372,22 @@ RLLM_EXPORT int rllm_latent_attention_mma(const void* q, void* out, const void* 
     return RLLM_E_UNSUPPORTED;
 #define LAM_GO(MT_, NVT_)                                                                                   \
   return lam_launch<MT_, NVT_>((const bf16*)q, (bf16*)out, (const bf16*)cache, block_table, max_blocks, q_start, \
-                               seq_lens, S, max_q, heads, dk, dv, page_size, num_pages, window, scale, sink, err, stream)
-  if (dv <= 32) LAM_GO(4, 1);
-  if (dv <= 64) LAM_GO(4, 2);
-  if (dv <= 128) LAM_GO(4, 4);
-  if (dv <= 256) LAM_GO(4, 8);
-  LAM_GO(2, 16);
+                               seq_lens, S, max_q, heads, dk, dv, page_size, num_pages, window, scale, sink,   \
+                               split_tiles, nsplit, work, err, stream)
+  // as many row tiles of 16 as the sequences' rows fill, up to what the accumulators leave room for
+  const long long rows = (long long)max_q * heads;
+  const int mt = rows <= 16 ? 1 : (rows <= 32 ? 2 : 4);
+#define LAM_PICK(NVT_, MAXMT_)                           \
+  do {                                                   \
+    if (mt == 1) LAM_GO(1, NVT_);                        \
+    if (mt == 2 || MAXMT_ == 2) LAM_GO(2, NVT_);         \
+    LAM_GO(MAXMT_, NVT_);                                \
+  } while (0)
+  if (dv <= 32) LAM_PICK(1, 4);
+  if (dv <= 64) LAM_PICK(2, 4);
+  if (dv <= 128) LAM_PICK(4, 4);
+  if (dv <= 256) LAM_PICK(8, 4);
+  LAM_PICK(16, 2);
+#undef LAM_PICK
 #undef LAM_GO
 }

@@ -49,6 +49,99 @@ mingru_scan_kernel(const TA* __restrict__ zxg, int stride, const TW* __restrict_
   state[(size_t)slot * W + c] = S;
 }
 
+// Long portions: the sequence's tokens of this step are cut into chunks of MG_CHUNK.  The recurrence is
+// linear in the state, S_t = a_t S_{t-1} + b_t with a_t = 1 - z_t and b_t = z_t c_t, so a chunk is
+// summarised by (A, B) = (product of its a_t, its end state from a zero start): first every chunk
+// computes its (A, B) at once, then every chunk rebuilds its start state from the sequence's state and
+// the chunks before it (in order) and walks its tokens as the plain kernel does.  Results differ from the
+// plain kernel's by rounding only, and do not depend on what else is in the batch.
+#define MG_CHUNK 64
+
+template <typename TA, typename TW>
+__global__ void __launch_bounds__(MG_THREADS)
+mingru_chunk_summary_kernel(const TA* __restrict__ zxg, int stride, const TW* __restrict__ bz,
+                            const TW* __restrict__ bx, const float* __restrict__ state,
+                            const int* __restrict__ q_start, const int* __restrict__ slots, int num_slots,
+                            int max_chunks, float* __restrict__ carry, float* __restrict__ init, int W) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int s = blockIdx.y / max_chunks, k = blockIdx.y % max_chunks;
+  if (c >= W) return;
+  const int t0 = q_start[s] + k * MG_CHUNK, t1 = min(q_start[s + 1], t0 + MG_CHUNK);
+  if (t0 >= t1) return;
+  const int slot = slots[s];
+  if (slot < 0 || slot >= num_slots) return;
+  if (k == 0) init[(size_t)s * W + c] = state[(size_t)slot * W + c];
+  const float biasz = to_f32(bz[c]), biasx = to_f32(bx[c]);
+  float A = 1.f, B = 0.f;
+  for (int t = t0; t < t1; ++t) {
+    const TA* r = zxg + (size_t)t * stride + c;
+    const float z = sigmoid_f32(to_f32(r[0]) + biasz), u = to_f32(r[W]) + biasx;
+    const float cand = (u >= 0.f) ? u + 0.5f : sigmoid_f32(u);
+    A *= 1.0f - z;
+    B = fmaf(1.0f - z, B, z * cand);
+  }
+  float* o = carry + ((size_t)blockIdx.y * 2) * W + c;
+  o[0] = A;
+  o[W] = B;
+}
+
+template <typename TA, typename TW>
+__global__ void __launch_bounds__(MG_THREADS)
+mingru_chunk_scan_kernel(const TA* __restrict__ zxg, int stride, const TW* __restrict__ bz,
+                         const TW* __restrict__ bx, float* __restrict__ state, const int* __restrict__ q_start,
+                         const int* __restrict__ slots, int num_slots, int max_chunks,
+                         const float* __restrict__ carry, const float* __restrict__ init, TA* __restrict__ out,
+                         int W, int* __restrict__ err) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int s = blockIdx.y / max_chunks, k = blockIdx.y % max_chunks;
+  if (c >= W) return;
+  const int t0 = q_start[s] + k * MG_CHUNK, t1 = min(q_start[s + 1], t0 + MG_CHUNK);
+  if (t0 >= t1) return;
+  const int slot = slots[s];
+  if (slot < 0 || slot >= num_slots) {
+    atomicOr(err, 8);
+    return;
+  }
+  float S = init[(size_t)s * W + c];
+  for (int j = 0; j < k; ++j) {
+    const float* p = carry + ((size_t)(s * max_chunks + j) * 2) * W + c;
+    S = fmaf(p[0], S, p[W]);
+  }
+  const float biasz = to_f32(bz[c]), biasx = to_f32(bx[c]);
+  for (int t = t0; t < t1; ++t) {
+    const TA* r = zxg + (size_t)t * stride + c;
+    const float z = sigmoid_f32(to_f32(r[0]) + biasz), u = to_f32(r[W]) + biasx, g = to_f32(r[2 * W]);
+    const float cand = (u >= 0.f) ? u + 0.5f : sigmoid_f32(u);
+    S = fmaf(1.0f - z, S, z * cand);
+    out[(size_t)t * W + c] = from_f32<TA>(S * (g * sigmoid_f32(g)));
+  }
+  if (t1 == q_start[s + 1]) state[(size_t)slot * W + c] = S;
+}
+
+// work: float32 [S * max_chunks * 2 * W + S * W], max_chunks = ceil(max_q / 64)
+RLLM_EXPORT int rllm_mingru_scan_chunked(const void* zxg, int stride, const void* bz, const void* bx, float* state,
+                                         const int* q_start, const int* slots, int num_slots, void* out, int S,
+                                         int W, int max_q, float* work, int act_dtype, int w_dtype, int* err,
+                                         cudaStream_t stream) {
+  if (S <= 0 || max_q <= 0) return 0;
+  const int max_chunks = (max_q + MG_CHUNK - 1) / MG_CHUNK;
+  if (W <= 0 || stride < 3 * W || num_slots <= 0 || (long long)S * max_chunks > 65535) return RLLM_E_BADARG;
+  dim3 grid((W + MG_THREADS - 1) / MG_THREADS, S * max_chunks);
+  float* carry = work;
+  float* init = work + (size_t)S * max_chunks * 2 * W;
+#define MG_LAUNCH(TA, TW)                                                                                   \
+  do {                                                                                                      \
+    mingru_chunk_summary_kernel<TA, TW><<<grid, MG_THREADS, 0, stream>>>((const TA*)zxg, stride, (const TW*)bz, \
+        (const TW*)bx, state, q_start, slots, num_slots, max_chunks, carry, init, W);                       \
+    mingru_chunk_scan_kernel<TA, TW><<<grid, MG_THREADS, 0, stream>>>((const TA*)zxg, stride, (const TW*)bz, \
+        (const TW*)bx, state, q_start, slots, num_slots, max_chunks, carry, init, (TA*)out, W, err);        \
+  } while (0)
+  RLLM_DISPATCH_DTYPE(act_dtype, TA_, RLLM_DISPATCH_DTYPE(w_dtype, TW_, MG_LAUNCH(TA_, TW_)));
+#undef MG_LAUNCH
+  RLLM_LAUNCH_CHECK();
+  return 0;
+}
+
 RLLM_EXPORT int rllm_mingru_scan(const void* zxg, int stride, const void* bz, const void* bx, float* state,
                                  const int* q_start, const int* slots, int num_slots, void* out, int S, int W,
                                  int act_dtype, int w_dtype, int* err, cudaStream_t stream) {

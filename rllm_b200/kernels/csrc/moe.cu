@@ -49,7 +49,8 @@ moe_route_kernel(const T* __restrict__ h, const T* __restrict__ wr, int* __restr
     float best = -1.f;
     int bi = 0x7fffffff;
     for (int e = lane; e < E; e += 32) {
-      const float v = z[e];
+      float v = z[e];
+      if (v != v) v = 0.f;                 // a NaN score still leaves an expert index inside the range
       if (v > best) { best = v; bi = e; }
     }
 #pragma unroll
@@ -65,6 +66,57 @@ moe_route_kernel(const T* __restrict__ h, const T* __restrict__ wr, int* __restr
     }
     __syncwarp();
   }
+}
+
+// the same choice from logits that a matrix product left in float32: z [T, E]
+__global__ void __launch_bounds__(32 * ROUTE_WARPS)
+moe_choose_kernel(const float* __restrict__ logits, int* __restrict__ ids, float* __restrict__ weights,
+                  int T_tokens, int E, int top) {
+  extern __shared__ float zs[];   // [ROUTE_WARPS][E]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t = blockIdx.x * ROUTE_WARPS + warp;
+  if (t >= T_tokens) return;
+  float* z = zs + warp * E;
+  float mx = -INFINITY;
+  for (int e = lane; e < E; e += 32) { z[e] = logits[(size_t)t * E + e]; mx = fmaxf(mx, z[e]); }
+  mx = warp_max(mx);
+  float sum = 0.f;
+  for (int e = lane; e < E; e += 32) sum += expf(z[e] - mx);
+  sum = warp_sum(sum);
+  for (int e = lane; e < E; e += 32) z[e] = expf(z[e] - mx) / sum;
+  __syncwarp();
+  for (int k = 0; k < top; ++k) {
+    float best = -1.f;
+    int bi = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      float v = z[e];
+      if (v != v) v = 0.f;
+      if (v > best) { best = v; bi = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+    }
+    if (lane == 0) {
+      ids[(size_t)t * top + k] = bi;
+      weights[(size_t)t * top + k] = best;
+      z[bi] = -2.f;
+    }
+    __syncwarp();
+  }
+}
+
+RLLM_EXPORT int rllm_moe_choose(const float* logits, int* ids, float* weights, int T, int E, int top,
+                                cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (E <= 0 || top <= 0 || top > E || E > 2048) return RLLM_E_BADARG;
+  const unsigned blocks = (unsigned)((T + ROUTE_WARPS - 1) / ROUTE_WARPS);
+  moe_choose_kernel<<<blocks, 32 * ROUTE_WARPS, (size_t)ROUTE_WARPS * E * sizeof(float), stream>>>(
+      logits, ids, weights, T, E, top);
+  RLLM_LAUNCH_CHECK();
+  return 0;
 }
 
 RLLM_EXPORT int rllm_moe_route(const void* h, const void* wr, int* ids, float* weights, int T, int H, int E,
@@ -92,7 +144,7 @@ moe_sort_kernel(const int* __restrict__ ids, int P, int E, int bm, int* __restri
   int* cur = tstart + E + 1;
   for (int e = threadIdx.x; e < E; e += blockDim.x) { cnt[e] = 0; cur[e] = 0; }
   __syncthreads();
-  for (int p = threadIdx.x; p < P; p += blockDim.x) atomicAdd(&cnt[ids[p]], 1);
+  for (int p = threadIdx.x; p < P; p += blockDim.x) atomicAdd(&cnt[min(max(ids[p], 0), E - 1)], 1);
   __syncthreads();
   if (threadIdx.x == 0) {
     int a = 0, b = 0;
@@ -114,7 +166,7 @@ moe_sort_kernel(const int* __restrict__ ids, int P, int E, int bm, int* __restri
     }
   }
   for (int p = threadIdx.x; p < P; p += blockDim.x) {
-    const int e = ids[p];
+    const int e = min(max(ids[p], 0), E - 1);
     sorted[start[e] + atomicAdd(&cur[e], 1)] = p;
   }
 }

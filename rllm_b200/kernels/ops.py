@@ -682,13 +682,29 @@ def depth_average(history: torch.Tensor, levels: int, coeff: torch.Tensor, strea
 # ---------------------------------------------------------------------------
 # minGRU (mingru.cu)
 # ---------------------------------------------------------------------------
+MINGRU_CHUNKED_FROM = 129      # a step whose longest portion has at least this many tokens scans in chunks
+
+
 def mingru_scan(zxg: torch.Tensor, bias_z: torch.Tensor, bias_x: torch.Tensor, state: torch.Tensor,
                 q_start: torch.Tensor, slots: torch.Tensor, num_seqs: int, out: torch.Tensor,
-                err: torch.Tensor) -> None:
+                err: torch.Tensor, max_q_len: int = 1) -> None:
     """zxg [T, >= 3 W]: a token's z, x and g projections side by side; state float32 [slots, W], updated in
-    place for the sequences' slots; out [T, W] = S_t * silu(g)."""
+    place for the sequences' slots; out [T, W] = S_t * silu(g).  ``max_q_len``: the most tokens a sequence
+    brings; long portions are scanned in chunks of 64 that run side by side."""
     lib = build.load_library("mingru")
     T, W = out.shape
+    if max_q_len >= MINGRU_CHUNKED_FROM and num_seqs * -(-max_q_len // 64) <= 65535:
+        assert zxg.shape[0] == T and zxg.stride(1) == 1 and zxg.shape[1] >= 3 * W and out.dtype is zxg.dtype
+        assert state.dtype is torch.float32 and state.shape[1] == W and bias_z.dtype is bias_x.dtype
+        _contig(out, "out"); _contig(state, "state")
+        chunks = -(-max_q_len // 64)
+        work = torch.empty(num_seqs * chunks * 2 * W + num_seqs * W, dtype=torch.float32, device=out.device)
+        _check(lib.rllm_mingru_scan_chunked(_ptr(zxg), c_int(zxg.stride(0)), _ptr(bias_z), _ptr(bias_x), _ptr(state),
+                                            _ptr(q_start), _ptr(slots), c_int(state.shape[0]), _ptr(out),
+                                            c_int(num_seqs), c_int(W), c_int(max_q_len), _ptr(work),
+                                            c_int(dtype_code(out.dtype)), c_int(dtype_code(bias_z.dtype)),
+                                            _ptr(err), _stream()), "mingru_scan_chunked")
+        return
     assert zxg.shape[0] == T and zxg.stride(1) == 1 and zxg.shape[1] >= 3 * W and out.dtype is zxg.dtype
     assert state.dtype is torch.float32 and state.shape[1] == W
     assert bias_z.dtype is bias_x.dtype and bias_z.numel() == W and bias_x.numel() == W
@@ -780,6 +796,11 @@ def latent_attention_simt(q: torch.Tensor, out: torch.Tensor, cache: torch.Tenso
            "latent_attention_simt")
 
 
+LATENT_SPLIT_MAX_TILES = 64      # at most this many row tiles in a launch (they fill less than half the GPU) ...
+LATENT_SPLIT_MIN_KEYS = 1024     # ... and at least this many keys to walk: the keys are cut into splits too
+LATENT_SPLIT_KEYS = 256          # keys a split (a multiple of 32, at absolute positions)
+
+
 def latent_attention_mma_takes(dtype: torch.dtype, dk: int, dv: int) -> bool:
     """Whether the tensor-core kernel computes this attention (RLLM_LATENT_ATTENTION=simt keeps it on the CUDA cores)."""
     import os
@@ -790,11 +811,22 @@ def latent_attention_mma_takes(dtype: torch.dtype, dk: int, dv: int) -> bool:
 def latent_attention_mma(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                          q_start: torch.Tensor, seq_lens: torch.Tensor, num_seqs: int, max_q_len: int, heads: int,
                          dk: int, dv: int, window: int, scale: float, sink: Optional[torch.Tensor],
-                         err: torch.Tensor) -> None:
+                         err: torch.Tensor, max_seq_len: int = 0) -> None:
     """The same attention as ``latent_attention_simt`` on the tensor cores, for bfloat16.  Sequence s owns
     tokens q_start[s] .. q_start[s+1], the last of them at position seq_lens[s] - 1; ``max_q_len``: the most
-    tokens a sequence brings (sizes the grid)."""
+    tokens a sequence brings (sizes the grid).  ``max_seq_len`` (an upper bound of seq_lens, 0: unknown): with
+    few rows and long sequences the keys are also cut into splits of 256 that run side by side."""
     lib = build.load_library("latent_attention_mma")
+    split_tiles, nsplit, work = 0, 1, None
+    row_tiles = num_seqs * -(-(max_q_len * heads) // 64)
+    keys = min(max_seq_len, window + max_q_len) if window else max_seq_len
+    if row_tiles <= LATENT_SPLIT_MAX_TILES and keys >= LATENT_SPLIT_MIN_KEYS:
+        split_tiles = LATENT_SPLIT_KEYS // 32
+        nsplit = -(-(-(-max_seq_len // 32)) // split_tiles)
+        lib.rllm_latent_attention_mma_work.restype = c_longlong
+        n = int(lib.rllm_latent_attention_mma_work(c_int(num_seqs), c_int(max_q_len), c_int(heads), c_int(dv),
+                                                   c_int(nsplit)))
+        work = torch.empty(n, dtype=torch.float32, device=q.device)
     T = q.shape[0]
     assert q.shape == (T, heads * dk) and out.shape == (T, heads * dv) and cache.shape[3] == dk
     assert q.dtype is torch.bfloat16 and cache.dtype is torch.bfloat16 and out.dtype is torch.bfloat16
@@ -804,8 +836,9 @@ def latent_attention_mma(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor
     _check(lib.rllm_latent_attention_mma(_ptr(q), _ptr(out), _ptr(cache), _ptr(block_table),
                                          c_int(block_table.shape[1]), _ptr(q_start), _ptr(seq_lens), c_int(num_seqs),
                                          c_int(max_q_len), c_int(heads), c_int(dk), c_int(dv), c_int(cache.shape[2]),
-                                         c_int(cache.shape[0]), c_int(window), c_float(scale), _ptr(sink), _ptr(err),
-                                         _stream()), "latent_attention_mma")
+                                         c_int(cache.shape[0]), c_int(window), c_float(scale), _ptr(sink),
+                                         c_int(split_tiles), c_int(nsplit), _ptr(work), _ptr(err), _stream()),
+           "latent_attention_mma")
 
 
 # ---------------------------------------------------------------------------
@@ -826,6 +859,19 @@ def moe_route(h: torch.Tensor, w_router: torch.Tensor, top: int):
     scores = torch.empty((T, top), dtype=torch.float32, device=h.device)
     _check(lib.rllm_moe_route(_ptr(h), _ptr(w_router), _ptr(ids), _ptr(scores), c_int(T), c_int(H), c_int(E),
                               c_int(top), c_int(dtype_code(h.dtype)), _stream()), "moe_route")
+    return ids, scores
+
+
+def moe_choose(logits: torch.Tensor, top: int):
+    """``moe_route`` from router logits that a matrix product left in float32 [T, E]."""
+    lib = build.load_library("moe")
+    T, E = logits.shape
+    assert logits.dtype is torch.float32
+    _contig(logits, "logits")
+    ids = torch.empty((T, top), dtype=torch.int32, device=logits.device)
+    scores = torch.empty((T, top), dtype=torch.float32, device=logits.device)
+    _check(lib.rllm_moe_choose(_ptr(logits), _ptr(ids), _ptr(scores), c_int(T), c_int(E), c_int(top), _stream()),
+           "moe_choose")
     return ids, scores
 
 

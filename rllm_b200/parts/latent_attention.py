@@ -124,7 +124,8 @@ class LatentAttention(Mixer):
         o = torch.empty((T, H * self.kv_rank), dtype=x.dtype, device=x.device)
         if ops.latent_attention_mma_takes(x.dtype, dk, self.kv_rank):
             ops.latent_attention_mma(qt, o, cache.k, table, ctx.q_start, ctx.seq_lens, ctx.num_seqs, ctx.max_q_len, H,
-                                     dk, self.kv_rank, int(self.window or 0), self.scale, self.sink, ctx.err)
+                                     dk, self.kv_rank, int(self.window or 0), self.scale, self.sink, ctx.err,
+                                     max_seq_len=ctx.max_seq_len)
         else:
             ops.latent_attention_simt(qt, o, cache.k, table, ctx.positions, ctx.token_seq, H, dk, self.kv_rank,
                                       int(self.window or 0), self.scale, self.sink, ctx.err)

@@ -65,5 +65,6 @@ class MinGRU(Mixer):
     def forward(self, x, ctx: StepContext, cache: StateCacheView):
         a = linear(x, self.w_in)                                   # [T, 3 width]: z | x | g
         out = torch.empty((x.shape[0], self.width), dtype=x.dtype, device=x.device)
-        ops.mingru_scan(a, self.b_z, self.b_x, cache.state, ctx.q_start, ctx.state_slots, ctx.num_seqs, out, ctx.err)
+        ops.mingru_scan(a, self.b_z, self.b_x, cache.state, ctx.q_start, ctx.state_slots, ctx.num_seqs, out, ctx.err,
+                        max_q_len=ctx.max_q_len)
         return linear(out, self.w_o)

@@ -26,8 +26,12 @@ import torch
 
 from ..kernels import ops
 from .base import FeedForward
+from .linear import linear
 from .registry import register_part
 from .spec import PartSpec, TensorSpec
+
+
+ROUTE_FUSED_ROWS = 64      # up to here one kernel computes logits, softmax and choice of a token
 
 
 @register_part("feed_forward", "routed_experts")
@@ -71,7 +75,11 @@ class RoutedExperts(FeedForward):
         self.w_down = torch.stack([tensors[self._expert("down", e)] for e in range(self.experts)]).contiguous()
 
     def forward_slots(self, x: torch.Tensor):
-        ids, scores = ops.moe_route(x, self.w_router, self.top)
+        if x.shape[0] > ROUTE_FUSED_ROWS:
+            # many rows: the logits are one matrix product with a float32 result, the choice a small kernel
+            ids, scores = ops.moe_choose(linear(x, self.w_router, out_dtype=torch.float32), self.top)
+        else:
+            ids, scores = ops.moe_route(x, self.w_router, self.top)
         return ops.moe_experts(x, ids, self.w_gate_up, self.w_down, self.limit, self.alpha), scores
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:

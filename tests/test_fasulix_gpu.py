@@ -430,3 +430,81 @@ def test_greedy_generation_through_the_entry_point(fx_dirs, dtype):
     assert any(g.graph is not None for g in llm.engine.runner.graphs.values())
     llm.engine.cache.check()
     assert llm.engine.cache.usage()["num_requests"] == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_portions_scan_in_chunks_and_match_the_token_by_token_state(dtype):
+    """Two sequences of 300 and 131 tokens (chunks of 64 with ragged ends) beside one of 2 tokens, from a
+    non-zero state: outputs and final states against the recurrence written out."""
+    from rllm_b200.kernels import ops
+    torch.manual_seed(8)
+    W, lens, slots = 40, [300, 2, 131], [1, 2, 0]
+    T = sum(lens)
+    a = (torch.randn(T, 3 * W) * 2).to(DT[dtype])
+    bz, bx = torch.randn(W).to(DT[dtype]), torch.randn(W).to(DT[dtype])
+    state = torch.rand(4, W)
+    want_state = state.double().clone()
+    want = torch.zeros(T, W, dtype=torch.float64)
+    ad, off = a.double(), 0
+    for n, sl in zip(lens, slots):
+        s = want_state[sl].clone()
+        for t in range(off, off + n):
+            z = torch.sigmoid(ad[t, :W] + bz.double())
+            u = ad[t, W:2 * W] + bx.double()
+            s = (1 - z) * s + z * torch.where(u >= 0, u + 0.5, torch.sigmoid(u))
+            g = ad[t, 2 * W:]
+            want[t] = s * g * torch.sigmoid(g)
+        want_state[sl] = s
+        off += n
+    out = torch.empty(T, W, dtype=DT[dtype], device="cuda")
+    st = state.cuda()
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    q_start = torch.tensor([0, 300, 302, T], dtype=torch.int32, device="cuda")
+    ops.mingru_scan(a.cuda(), bz.cuda(), bx.cuda(), st, q_start, torch.tensor(slots, dtype=torch.int32, device="cuda"),
+                    3, out, err, max_q_len=300)
+    assert int(err.item()) == 0
+    assert rel(out, want) <= (2e-6 if dtype == "float32" else 1e-2)
+    assert rel(st, want_state) <= 2e-6
+    assert torch.equal(st[3].cpu(), state[3])
+
+
+@pytest.mark.parametrize("window,sink,heads,dk,dv", [(0, True, 2, 144, 128), (300, False, 6, 56, 48), (0, False, 16, 576, 512)])
+def test_decoding_over_long_rows_cuts_the_keys_into_splits(window, sink, heads, dk, dv):
+    """Two sequences of 1500 and 700 cached rows, one new token each: few rows, many keys, so the keys are cut
+    into splits of 256 whose partial sums a second kernel adds (with the sink)."""
+    from rllm_b200.kernels import ops
+    g = torch.Generator().manual_seed(dk)
+    page, lens = 16, [1500, 700]
+    n_pages = sum(-(-n // page) for n in lens)
+    cache = torch.zeros(n_pages + 1, 1, page, dk, dtype=torch.bfloat16)
+    table = torch.full((2, -(-max(lens) // page)), -1, dtype=torch.int32)
+    perm = torch.randperm(n_pages + 1, generator=g)
+    rows, used = [], 0
+    for s, n in enumerate(lens):
+        r = torch.randn(n, dk, generator=g).to(torch.bfloat16)
+        rows.append(r)
+        for b in range(-(-n // page)):
+            table[s, b] = perm[used]
+            cache[perm[used], 0, : min(page, n - b * page)] = r[b * page:(b + 1) * page]
+            used += 1
+    q = torch.randn(2, heads, dk, generator=g).to(torch.bfloat16)
+    sk = (torch.randn(heads, generator=g) + 1.0) if sink else None
+    scale = dk ** -0.5
+    out = torch.empty(2, heads * dv, dtype=torch.bfloat16, device="cuda")
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ops.latent_attention_mma(q.reshape(2, heads * dk).cuda(), out, cache.cuda(), table.cuda(),
+                             torch.tensor([0, 1, 2], dtype=torch.int32, device="cuda"),
+                             torch.tensor(lens, dtype=torch.int32, device="cuda"), 2, 1, heads, dk, dv, window, scale,
+                             sk.cuda() if sink else None, err, max_seq_len=1504)
+    assert int(err.item()) == 0
+    want = torch.zeros(2, heads, dv, dtype=torch.float64)
+    for s, n in enumerate(lens):
+        rd = rows[s].double()
+        lo = max(0, n - window) if window else 0
+        for h in range(heads):
+            sc = rd[lo:n] @ q[s, h].double() * scale
+            top = max(float(sc.max()), float(sk[h])) if sink else float(sc.max())
+            e = torch.exp(sc - top)
+            den = e.sum() + (math.exp(float(sk[h]) - top) if sink else 0.0)
+            want[s, h] = (e / den) @ rd[lo:n, :dv]
+    assert rel(out.view(2, heads, dv), want) <= 2e-2
