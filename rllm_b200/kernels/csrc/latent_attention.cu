@@ -36,12 +36,17 @@ __device__ __forceinline__ void rot_cos_sin<bf16>(int pos, double f, float* c, f
 
 template <typename T, typename TW>
 __global__ void __launch_bounds__(128)
-latent_prep_kernel(const T* __restrict__ a, int a_stride, int q_rank, int kv_rank, int rot, int rot_dims,
-                   const TW* __restrict__ wq, const TW* __restrict__ wkv, float eps, T* __restrict__ cq,
-                   T* __restrict__ cache, const int* __restrict__ block_table, int max_blocks,
-                   const int* __restrict__ positions, const int* __restrict__ token_seq,
-                   const double* __restrict__ inv_freq, int page_size, int num_pages, int write_kv,
-                   int* __restrict__ err) {
+latent_prep_kernel(const T* a, int a_stride, int q_rank, int kv_rank, int rot, int rot_dims,
+                   const TW* wq, const TW* wkv, float eps, T* cq,
+                   T* cache, const int* block_table, int max_blocks,
+                   const int* positions, const int* token_seq,
+                   const double* inv_freq, int page_size, int num_pages, int write_kv,
+                   int* err) {
+  // (Every kernel of this file starts with the wait for the kernel ahead of it in the stream and lets the
+  // next one in right after: launches overlap the tails of their predecessors.  The pointer parameters
+  // carry no __restrict__, so that no load is proved independent of that wait and moved above it.)
+  pdl_wait();
+  pdl_launch();
   __shared__ float red[32];
   const int t = blockIdx.x;
   const T* row = a + (size_t)t * a_stride;
@@ -92,7 +97,7 @@ RLLM_EXPORT int rllm_latent_prep(const void* a, int a_stride, int q_rank, int kv
                                    page_size <= 0 || num_pages <= 0 || max_blocks <= 0)))
     return RLLM_E_BADARG;
 #define LP_LAUNCH(T_, TW_)                                                                                \
-  latent_prep_kernel<T_, TW_><<<T, 128, 0, stream>>>((const T_*)a, a_stride, q_rank, kv_rank, rot, rot_dims, \
+  rllm_launch_pdl(latent_prep_kernel<T_, TW_>, dim3(T), dim3(128), (size_t)(0), stream, (const T_*)a, a_stride, q_rank, kv_rank, rot, rot_dims, \
       (const TW_*)wq, (const TW_*)wkv, eps, (T_*)cq, (T_*)cache, block_table, max_blocks, positions,      \
       token_seq, inv_freq, page_size, num_pages, write_kv, err)
   RLLM_DISPATCH_DTYPE(dtype, TT, RLLM_DISPATCH_DTYPE(w_dtype, TW, LP_LAUNCH(TT, TW)));
@@ -105,9 +110,11 @@ RLLM_EXPORT int rllm_latent_prep(const void* a, int a_stride, int q_rank, int kv
 // the queries' rotated part: q[t, h, dim : dim+rot] rotated -> qt[t, h, kv_rank : kv_rank+rot]
 // ---------------------------------------------------------------------------
 template <typename T>
-__global__ void latent_q_rot_kernel(const T* __restrict__ q, T* __restrict__ qt, const int* __restrict__ positions,
-                                    const double* __restrict__ inv_freq, int heads, int dim, int rot,
+__global__ void latent_q_rot_kernel(const T* q, T* qt, const int* positions,
+                                    const double* inv_freq, int heads, int dim, int rot,
                                     int rot_dims, int kv_rank, long long total) {
+  pdl_wait();
+  pdl_launch();
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   const int half = rot / 2;
@@ -136,7 +143,7 @@ RLLM_EXPORT int rllm_latent_q_rot(const void* q, void* qt, const int* positions,
   if (total <= 0) return 0;
   if (rot & 1 || rot_dims > rot || (rot_dims & 1)) return RLLM_E_BADARG;
   const unsigned blocks = (unsigned)((total + 255) / 256);
-  RLLM_DISPATCH_DTYPE(dtype, TT, (latent_q_rot_kernel<TT><<<blocks, 256, 0, stream>>>(
+  RLLM_DISPATCH_DTYPE(dtype, TT, (rllm_launch_pdl(latent_q_rot_kernel<TT>, dim3(blocks), dim3(256), (size_t)(0), stream, 
       (const TT*)q, (TT*)qt, positions, inv_freq, heads, dim, rot, rot_dims, kv_rank, total)));
   RLLM_LAUNCH_CHECK();
   return 0;
@@ -148,8 +155,10 @@ RLLM_EXPORT int rllm_latent_q_rot(const void* q, void* qt, const int* positions,
 // ---------------------------------------------------------------------------
 template <typename T, int BM, bool B_KN>
 __global__ void __launch_bounds__(TG_THREADS)
-head_gemm_kernel(const T* __restrict__ A, long long lda, long long a_head, const T* __restrict__ B, long long ldb,
-                 long long b_head, T* __restrict__ C, long long ldc, long long c_head, int M, int N, int K) {
+head_gemm_kernel(const T* A, long long lda, long long a_head, const T* B, long long ldb,
+                 long long b_head, T* C, long long ldc, long long c_head, int M, int N, int K) {
+  pdl_wait();
+  pdl_launch();
   __shared__ TileGemmSmem<BM> sm;
   const int h = blockIdx.z, m0 = blockIdx.y * BM, n0 = blockIdx.x * TG_BN;
   if (threadIdx.x < BM) {
@@ -174,10 +183,12 @@ head_gemm_kernel(const T* __restrict__ A, long long lda, long long a_head, const
 
 template <int BM>
 __global__ void __launch_bounds__(TGM_THREADS)
-head_gemm_mma_kernel(const bf16* __restrict__ A, long long lda, long long a_head, const bf16* __restrict__ B,
-                     long long ldb, long long b_head, bf16* __restrict__ C, long long ldc, long long c_head, int M,
+head_gemm_mma_kernel(const bf16* A, long long lda, long long a_head, const bf16* B,
+                     long long ldb, long long b_head, bf16* C, long long ldc, long long c_head, int M,
                      int N, int K) {
-  __shared__ __align__(16) MmaTileSmem<BM, 1> sm;
+  pdl_wait();
+  pdl_launch();
+  MmaTileSmem<BM, 1>& sm = tgm_smem<BM, 1>();
   const int h = blockIdx.z, m0 = blockIdx.y * BM, n0 = blockIdx.x * TGM_BN;
   if (threadIdx.x < BM) {
     const int m = m0 + threadIdx.x;
@@ -211,16 +222,16 @@ RLLM_EXPORT int rllm_head_gemm(const void* A, long long lda, long long a_head, c
   if (dtype == RLLM_DT_BF16 && !b_kn && !tgm_disabled() && K % 8 == 0 && lda % 8 == 0 && a_head % 8 == 0 &&
       ldb % 8 == 0 && b_head % 8 == 0 && (((uintptr_t)A | (uintptr_t)B) & 15) == 0) {
     if (small)
-      head_gemm_mma_kernel<16><<<grid, TGM_THREADS, 0, stream>>>((const bf16*)A, lda, a_head, (const bf16*)B, ldb,
+      rllm_launch_pdl(head_gemm_mma_kernel<16>, dim3(grid), dim3(TGM_THREADS), (size_t)(sizeof(MmaTileSmem<16, 1>)), stream, (const bf16*)A, lda, a_head, (const bf16*)B, ldb,
                                                                  b_head, (bf16*)C, ldc, c_head, M, N, K);
     else
-      head_gemm_mma_kernel<64><<<grid, TGM_THREADS, 0, stream>>>((const bf16*)A, lda, a_head, (const bf16*)B, ldb,
+      rllm_launch_pdl(head_gemm_mma_kernel<64>, dim3(grid), dim3(TGM_THREADS), (size_t)(sizeof(MmaTileSmem<64, 1>)), stream, (const bf16*)A, lda, a_head, (const bf16*)B, ldb,
                                                                  b_head, (bf16*)C, ldc, c_head, M, N, K);
     RLLM_LAUNCH_CHECK();
     return 0;
   }
 #define HG_LAUNCH(T_, BM_, KN_)                                                                          \
-  head_gemm_kernel<T_, BM_, KN_><<<grid, TG_THREADS, 0, stream>>>((const T_*)A, lda, a_head, (const T_*)B, \
+  rllm_launch_pdl(head_gemm_kernel<T_, BM_, KN_>, dim3(grid), dim3(TG_THREADS), (size_t)(0), stream, (const T_*)A, lda, a_head, (const T_*)B, \
       ldb, b_head, (T_*)C, ldc, c_head, M, N, K)
   RLLM_DISPATCH_DTYPE(dtype, TT, {
     if (small) { if (b_kn) HG_LAUNCH(TT, 16, true); else HG_LAUNCH(TT, 16, false); }
@@ -240,11 +251,13 @@ RLLM_EXPORT int rllm_head_gemm(const void* A, long long lda, long long a_head, c
 
 template <typename T, int R>
 __global__ void __launch_bounds__(32 * LA_WARPS)
-latent_attention_simt_kernel(const T* __restrict__ q, T* __restrict__ out, const T* __restrict__ cache,
-                             const int* __restrict__ block_table, int max_blocks,
-                             const int* __restrict__ positions, const int* __restrict__ token_seq, int T_tokens,
+latent_attention_simt_kernel(const T* q, T* out, const T* cache,
+                             const int* block_table, int max_blocks,
+                             const int* positions, const int* token_seq, int T_tokens,
                              int heads, int dk, int dv, int page_size, int num_pages, int window, float scale,
-                             const float* __restrict__ sink, int* __restrict__ err) {
+                             const float* sink, int* err) {
+  pdl_wait();
+  pdl_launch();
   extern __shared__ float qs[];  // [LA_WARPS][dk]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const long long gw = (long long)blockIdx.x * LA_WARPS + warp;
@@ -344,7 +357,7 @@ RLLM_EXPORT int rllm_latent_attention_simt(const void* q, void* out, const void*
   const unsigned blocks = (unsigned)((warps + LA_WARPS - 1) / LA_WARPS);
   const size_t smem = (size_t)LA_WARPS * dk * sizeof(float);
 #define LA_LAUNCH(T_, R_)                                                                                   \
-  latent_attention_simt_kernel<T_, R_><<<blocks, 32 * LA_WARPS, smem, stream>>>((const T_*)q, (T_*)out,     \
+  rllm_launch_pdl(latent_attention_simt_kernel<T_, R_>, dim3(blocks), dim3(32 * LA_WARPS), (size_t)(smem), stream, (const T_*)q, (T_*)out,     \
       (const T_*)cache, block_table, max_blocks, positions, token_seq, T, heads, dk, dv, page_size, num_pages, \
       window, scale, sink, err)
   RLLM_DISPATCH_DTYPE(dtype, TT, {

@@ -14,15 +14,15 @@
 // sink[h] and its sum at 1.  Exponentials are base 2 with log2(e) folded into the scale.
 //
 // Few rows and many keys (decoding): the key tiles are also cut into splits of
-// `split_tiles` tiles at absolute tile numbers, one CTA each (grid z); a split leaves
+// `split_keys` keys at absolute positions, one CTA each (grid z); a split leaves
 // its unnormalised sums, running max and sum in a work buffer and a second kernel
 // adds the splits of a row in order (and the sink).  Where the cuts fall depends on
 // the row's own sequence only.
 #include "common.cuh"
 #include <math.h>
 
-#define LAM_THREADS 128
-#define LAM_KEYS 32
+// NW warps a CTA (4, or 8 where the values are wider than 256: their columns are shared out among more
+// warps); a key tile has 8 keys a warp.
 
 __device__ __forceinline__ void lam_cp16(void* smem_dst, const void* src, bool valid) {
   const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
@@ -35,21 +35,26 @@ __device__ __forceinline__ void lam_mma(float (&c)[4], const uint32_t (&a)[4], u
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-template <int MT, int NVT>
-__global__ void __launch_bounds__(LAM_THREADS)
-latent_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const bf16* __restrict__ cache,
-                            const int* __restrict__ block_table, int max_blocks, const int* __restrict__ q_start,
-                            const int* __restrict__ seq_lens, int heads, int dk, int dv, int ld, int page_size,
-                            int num_pages, int window, float scale_log2, const float* __restrict__ sink,
-                            int split_tiles, float* __restrict__ work, int* __restrict__ err) {
-  constexpr int ROWS = 16 * MT;
+template <int MT, int NVT, int NW>
+__global__ void __launch_bounds__(32 * NW)
+latent_attention_mma_kernel(const bf16* q, bf16* out, const bf16* cache,
+                            const int* block_table, int max_blocks, const int* q_start,
+                            const int* seq_lens, int heads, int dk, int dv, int ld, int page_size,
+                            int num_pages, int window, float scale_log2, const float* sink,
+                            int split_keys, float* work, int* err) {
+  // (Every kernel of this file starts with the wait for the kernel ahead of it in the stream and lets the
+  // next one in right after: launches overlap the tails of their predecessors.  The pointer parameters
+  // carry no __restrict__, so that no load is proved independent of that wait and moved above it.)
+  pdl_wait();
+  pdl_launch();
+  constexpr int ROWS = 16 * MT, LAM_THREADS = 32 * NW, LAM_KEYS = 8 * NW;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* Qs = (bf16*)smem_raw;                               // [ROWS][ld]
   bf16* Ks = Qs + (size_t)ROWS * ld;                        // [2][LAM_KEYS][ld]
   bf16* Ps = Ks + (size_t)2 * LAM_KEYS * ld;                // [ROWS][LAM_KEYS + 8]
-  float* wmax = (float*)(Ps + ROWS * (LAM_KEYS + 8));       // [2][4][ROWS]
-  float* wsum = wmax + 2 * 4 * ROWS;                        // [2][4][ROWS]
-  float* m_cur = wsum + 2 * 4 * ROWS;                       // [ROWS]
+  float* wmax = (float*)(Ps + ROWS * (LAM_KEYS + 8));       // [2][NW][ROWS]
+  float* wsum = wmax + 2 * NW * ROWS;                       // [2][NW][ROWS]
+  float* m_cur = wsum + 2 * NW * ROWS;                      // [ROWS]
   float* l_cur = m_cur + ROWS;                              // [ROWS]
 
   const int s = blockIdx.y;
@@ -63,8 +68,9 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, 
   const int p_lo = pos0 + tok_lo, p_hi = pos0 + tok_hi;
   const int k_lo = (window > 0 && p_lo - window + 1 > 0) ? p_lo - window + 1 : 0;
   int tile_lo = k_lo / LAM_KEYS, tile_hi = p_hi / LAM_KEYS;           // inclusive
-  const int dvp = 32 * NVT;
+  const int dvp = 8 * NVT * NW;
   float* wrow = nullptr;              // split mode: where this CTA's rows leave their partial results
+  const int split_tiles = split_keys / LAM_KEYS;
   if (split_tiles > 0) {
     tile_lo = max(tile_lo, (int)blockIdx.z * split_tiles);
     tile_hi = min(tile_hi, (int)(blockIdx.z + 1) * split_tiles - 1);
@@ -91,7 +97,7 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, 
   }
   if (tid < ROWS) {
     const int h = (row_base + tid) % heads;
-    const bool with_sink = sink != nullptr && split_tiles <= 0;      // split mode: the merge adds the sink
+    const bool with_sink = sink != nullptr && split_keys <= 0;      // split mode: the merge adds the sink
     m_cur[tid] = with_sink ? sink[h] * 1.4426950408889634f : -INFINITY;
     l_cur[tid] = with_sink ? 1.f : 0.f;
   }
@@ -136,7 +142,7 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, 
     }
 
   load_keys(tile_lo, 0);
-  const int ksteps = (dk + 15) / 16;
+  const int ksteps = (dk + 31) / 32 * 2;                    // in pairs; the rows are zero beyond dk
   for (int tile = tile_lo; tile <= tile_hi; ++tile) {
     const int st = (tile - tile_lo) & 1, par = st;
     asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -149,23 +155,29 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, 
     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
       for (int i = 0; i < 4; ++i) sc[mt][i] = 0.f;
-    const bf16* kr = K + (size_t)(warp * 8 + g) * ld + 2 * t;
-    for (int ks = 0; ks < ksteps; ++ks) {
-      const uint32_t b0 = *(const uint32_t*)(kr + ks * 16), b1 = *(const uint32_t*)(kr + ks * 16 + 8);
+    // two k steps of 16 a round: one ldmatrix.x4 brings the keys' fragments of both (8 keys x 32 values),
+    // one ldmatrix.x4 per row tile and k step the queries'
+    const unsigned kaddr = (unsigned)__cvta_generic_to_shared(K + (size_t)(warp * 8 + (lane & 7)) * ld + (lane >> 3) * 8);
+    const unsigned qaddr = (unsigned)__cvta_generic_to_shared(Qs + (size_t)(lane & 15) * ld + (lane >> 4) * 8);
+    for (int ks = 0; ks < ksteps; ks += 2) {
+      uint32_t b[4];
+      asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                   : "=r"(b[0]), "=r"(b[1]), "=r"(b[2]), "=r"(b[3]) : "r"(kaddr + ks * 32));
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) {
-        const bf16* qr = Qs + (size_t)(mt * 16 + g) * ld + ks * 16 + 2 * t;
-        uint32_t a[4];
-        a[0] = *(const uint32_t*)qr;
-        a[1] = *(const uint32_t*)(qr + 8 * ld);
-        a[2] = *(const uint32_t*)(qr + 8);
-        a[3] = *(const uint32_t*)(qr + 8 * ld + 8);
-        lam_mma(sc[mt], a, b0, b1);
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t a[4];
+          asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                       : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3])
+                       : "r"(qaddr + (unsigned)((mt * 16 * ld + (ks + half) * 16) * 2)));
+          lam_mma(sc[mt], a, b[2 * half], b[2 * half + 1]);
+        }
       }
     }
     const int jbase = tile * LAM_KEYS + warp * 8 + 2 * t;
-    float* wm = wmax + (size_t)par * 4 * ROWS;
-    float* ws = wsum + (size_t)par * 4 * ROWS;
+    float* wm = wmax + (size_t)par * NW * ROWS;
+    float* ws = wsum + (size_t)par * NW * ROWS;
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
@@ -193,7 +205,9 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, 
       for (int hf = 0; hf < 2; ++hf) {
         const int r = mt * 16 + g + 8 * hf;
         const float mo = m_cur[r];
-        const float mn = fmaxf(fmaxf(mo, fmaxf(wm[r], wm[ROWS + r])), fmaxf(wm[2 * ROWS + r], wm[3 * ROWS + r]));
+        float mn = mo;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) mn = fmaxf(mn, wm[w * ROWS + r]);
         corr[mt][hf] = (mn == -INFINITY) ? 1.f : exp2f(mo - mn);
         float p0 = 0.f, p1 = 0.f;
         if (mn != -INFINITY) {
@@ -210,9 +224,14 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, 
     if (tid < ROWS) {
       const int r = tid;
       const float mo = m_cur[r];
-      const float mn = fmaxf(fmaxf(mo, fmaxf(wm[r], wm[ROWS + r])), fmaxf(wm[2 * ROWS + r], wm[3 * ROWS + r]));
+      float mn = mo, sum = 0.f;
+#pragma unroll
+      for (int w = 0; w < NW; ++w) {
+        mn = fmaxf(mn, wm[w * ROWS + r]);
+        sum += ws[w * ROWS + r];
+      }
       if (mn != -INFINITY) {
-        l_cur[r] = l_cur[r] * exp2f(mo - mn) + ((ws[r] + ws[ROWS + r]) + (ws[2 * ROWS + r] + ws[3 * ROWS + r]));
+        l_cur[r] = l_cur[r] * exp2f(mo - mn) + sum;
         m_cur[r] = mn;
       }
     }
@@ -229,11 +248,10 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, 
       uint32_t a[MT][4];
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) {
-        const bf16* pr = Ps + (size_t)(mt * 16 + g) * (LAM_KEYS + 8) + kk + 2 * t;
-        a[mt][0] = *(const uint32_t*)pr;
-        a[mt][1] = *(const uint32_t*)(pr + 8 * (LAM_KEYS + 8));
-        a[mt][2] = *(const uint32_t*)(pr + 8);
-        a[mt][3] = *(const uint32_t*)(pr + 8 * (LAM_KEYS + 8) + 8);
+        const unsigned paddr = (unsigned)__cvta_generic_to_shared(
+            Ps + (size_t)(mt * 16 + (lane & 15)) * (LAM_KEYS + 8) + kk + (lane >> 4) * 8);
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(a[mt][0]), "=r"(a[mt][1]), "=r"(a[mt][2]), "=r"(a[mt][3]) : "r"(paddr));
       }
 #pragma unroll
       for (int nt = 0; nt < NVT; ++nt) {
@@ -282,8 +300,10 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, 
 
 // one warp per (sequence, row): the splits' partial results in order, and the sink
 __global__ void __launch_bounds__(128)
-latent_attention_merge_kernel(const float* __restrict__ work, bf16* __restrict__ out, const int* __restrict__ q_start,
-                              int heads, int dv, int dvp, int max_rows, int nsplit, const float* __restrict__ sink) {
+latent_attention_merge_kernel(const float* work, bf16* out, const int* q_start,
+                              int heads, int dv, int dvp, int max_rows, int nsplit, const float* sink) {
+  pdl_wait();
+  pdl_launch();
   const int lane = threadIdx.x & 31;
   const int row = blockIdx.x * 4 + (threadIdx.x >> 5), s = blockIdx.y;
   const int t0 = q_start[s], nq = q_start[s + 1] - t0;
@@ -317,30 +337,30 @@ latent_attention_merge_kernel(const float* __restrict__ work, bf16* __restrict__
   }
 }
 
-template <int MT, int NVT>
+template <int MT, int NVT, int NW>
 static int lam_launch(const bf16* q, bf16* out, const bf16* cache, const int* block_table, int max_blocks,
                       const int* q_start, const int* seq_lens, int S, int max_q, int heads, int dk, int dv,
-                      int page_size, int num_pages, int window, float scale, const float* sink, int split_tiles,
+                      int page_size, int num_pages, int window, float scale, const float* sink, int split_keys,
                       int nsplit, float* work, int* err, cudaStream_t stream) {
-  constexpr int ROWS = 16 * MT;
-  const int dkp = (dk + 15) / 16 * 16;
-  const int ld = max(dkp, 32 * NVT) + 8;
+  constexpr int ROWS = 16 * MT, LAM_THREADS = 32 * NW, LAM_KEYS = 8 * NW;
+  const int dkp = (dk + 31) / 32 * 32;
+  const int ld = max(dkp, 8 * NVT * NW) + 8;
   const size_t smem = ((size_t)ROWS * ld + 2 * LAM_KEYS * ld + ROWS * (LAM_KEYS + 8)) * sizeof(bf16) +
-                      (size_t)(2 * 4 * ROWS * 2 + 2 * ROWS) * sizeof(float);
+                      (size_t)(2 * NW * ROWS * 2 + 2 * ROWS) * sizeof(float);
   if (smem > 220 * 1024) return RLLM_E_UNSUPPORTED;
   if (smem > 48 * 1024)
-    cudaFuncSetAttribute(latent_attention_mma_kernel<MT, NVT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaFuncSetAttribute(latent_attention_mma_kernel<MT, NVT, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   const long long blocks_x = ((long long)max_q * heads + ROWS - 1) / ROWS;
   if (blocks_x > 2147483647LL || S > 65535) return RLLM_E_UNSUPPORTED;
-  dim3 grid((unsigned)blocks_x, S, split_tiles > 0 ? nsplit : 1);
-  latent_attention_mma_kernel<MT, NVT><<<grid, LAM_THREADS, smem, stream>>>(
+  dim3 grid((unsigned)blocks_x, S, split_keys > 0 ? nsplit : 1);
+  rllm_launch_pdl(latent_attention_mma_kernel<MT, NVT, NW>, dim3(grid), dim3(LAM_THREADS), (size_t)(smem), stream, 
       q, out, cache, block_table, max_blocks, q_start, seq_lens, heads, dk, dv, ld, page_size, num_pages, window,
-      scale * 1.4426950408889634f, sink, split_tiles, work, err);
+      scale * 1.4426950408889634f, sink, split_keys, work, err);
   RLLM_LAUNCH_CHECK();
-  if (split_tiles > 0) {
+  if (split_keys > 0) {
     const int max_rows = (int)blocks_x * ROWS;
     dim3 mg((max_rows + 3) / 4, S);
-    latent_attention_merge_kernel<<<mg, 128, 0, stream>>>(work, out, q_start, heads, dv, 32 * NVT, max_rows, nsplit, sink);
+    rllm_launch_pdl(latent_attention_merge_kernel, dim3(mg), dim3(128), (size_t)(0), stream, work, out, q_start, heads, dv, 8 * NVT * NW, max_rows, nsplit, sink);
     RLLM_LAUNCH_CHECK();
   }
   return 0;
@@ -361,33 +381,33 @@ RLLM_EXPORT long long rllm_latent_attention_mma_work(int S, int max_q, int heads
 RLLM_EXPORT int rllm_latent_attention_mma(const void* q, void* out, const void* cache, const int* block_table,
                                           int max_blocks, const int* q_start, const int* seq_lens, int S, int max_q,
                                           int heads, int dk, int dv, int page_size, int num_pages, int window,
-                                          float scale, const float* sink, int split_tiles, int nsplit, float* work,
+                                          float scale, const float* sink, int split_keys, int nsplit, float* work,
                                           int* err, cudaStream_t stream) {
   if (S <= 0 || max_q <= 0) return 0;
-  if (split_tiles > 0 && (nsplit <= 0 || nsplit > 65535 || work == nullptr)) return RLLM_E_BADARG;
+  if (split_keys > 0 && (split_keys % 64 != 0 || nsplit <= 0 || nsplit > 65535 || work == nullptr)) return RLLM_E_BADARG;
   if (heads <= 0 || dk <= 0 || dv <= 0 || dv > dk || page_size <= 0 || num_pages <= 0 || max_blocks <= 0 ||
       window < 0)
     return RLLM_E_BADARG;
   if (dk % 8 != 0 || dv > 512 || (((uintptr_t)q | (uintptr_t)out | (uintptr_t)cache) & 15) != 0)
     return RLLM_E_UNSUPPORTED;
-#define LAM_GO(MT_, NVT_)                                                                                   \
-  return lam_launch<MT_, NVT_>((const bf16*)q, (bf16*)out, (const bf16*)cache, block_table, max_blocks, q_start, \
+#define LAM_GO(MT_, NVT_, NW_)                                                                              \
+  return lam_launch<MT_, NVT_, NW_>((const bf16*)q, (bf16*)out, (const bf16*)cache, block_table, max_blocks, q_start, \
                                seq_lens, S, max_q, heads, dk, dv, page_size, num_pages, window, scale, sink,   \
-                               split_tiles, nsplit, work, err, stream)
+                               split_keys, nsplit, work, err, stream)
   // as many row tiles of 16 as the sequences' rows fill, up to what the accumulators leave room for
   const long long rows = (long long)max_q * heads;
   const int mt = rows <= 16 ? 1 : (rows <= 32 ? 2 : 4);
-#define LAM_PICK(NVT_, MAXMT_)                           \
+#define LAM_PICK(NVT_, MAXMT_, NW_)                      \
   do {                                                   \
-    if (mt == 1) LAM_GO(1, NVT_);                        \
-    if (mt == 2 || MAXMT_ == 2) LAM_GO(2, NVT_);         \
-    LAM_GO(MAXMT_, NVT_);                                \
+    if (mt == 1) LAM_GO(1, NVT_, NW_);                   \
+    if (mt == 2 || MAXMT_ == 2) LAM_GO(2, NVT_, NW_);    \
+    LAM_GO(MAXMT_, NVT_, NW_);                           \
   } while (0)
-  if (dv <= 32) LAM_PICK(1, 4);
-  if (dv <= 64) LAM_PICK(2, 4);
-  if (dv <= 128) LAM_PICK(4, 4);
-  if (dv <= 256) LAM_PICK(8, 4);
-  LAM_PICK(16, 2);
+  if (dv <= 32) LAM_PICK(1, 4, 4);
+  if (dv <= 64) LAM_PICK(2, 4, 4);
+  if (dv <= 128) LAM_PICK(4, 4, 4);
+  if (dv <= 256) LAM_PICK(8, 4, 4);
+  LAM_PICK(8, 2, 8);
 #undef LAM_PICK
 #undef LAM_GO
 }

@@ -17,10 +17,15 @@
 
 template <typename TA, typename TW>
 __global__ void __launch_bounds__(GLUE_THREADS)
-gated_postnorm_add_kernel(const float* __restrict__ x_in, float* __restrict__ x_out, const TA* __restrict__ y,
-                          int slots, const float* __restrict__ slot_w, const TA* __restrict__ g, int g_stride,
-                          const TW* __restrict__ gb, const TW* __restrict__ nw, float eps,
-                          const TW* __restrict__ next_w, TA* __restrict__ next_out, float next_eps, int H) {
+gated_postnorm_add_kernel(const float* x_in, float* x_out, const TA* y,
+                          int slots, const float* slot_w, const TA* g, int g_stride,
+                          const TW* gb, const TW* nw, float eps,
+                          const TW* next_w, TA* next_out, float next_eps, int H) {
+  // (Every kernel of this file starts with the wait for the kernel ahead of it in the stream and lets the
+  // next one in right after: launches overlap the tails of their predecessors.  The pointer parameters
+  // carry no __restrict__, so that no load is proved independent of that wait and moved above it.)
+  pdl_wait();
+  pdl_launch();
   extern __shared__ float row[];
   __shared__ float red[32];
   const int t = blockIdx.x;
@@ -70,7 +75,7 @@ RLLM_EXPORT int rllm_gated_postnorm_add(const float* x_in, float* x_out, const v
     if (smem > 48 * 1024)                                                                                \
       cudaFuncSetAttribute(gated_postnorm_add_kernel<TA, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                            (int)smem);                                                                   \
-    gated_postnorm_add_kernel<TA, TW><<<T, GLUE_THREADS, smem, stream>>>(                                \
+    rllm_launch_pdl(gated_postnorm_add_kernel<TA, TW>, dim3(T), dim3(GLUE_THREADS), (size_t)(smem), stream,                                 \
         x_in, x_out, (const TA*)y, slots, slot_w, (const TA*)g, g_stride, (const TW*)gb, (const TW*)nw,  \
         eps, (const TW*)next_w, (TA*)next_out, next_eps, H);                                             \
   } while (0)
@@ -82,9 +87,11 @@ RLLM_EXPORT int rllm_gated_postnorm_add(const float* x_in, float* x_out, const v
 
 template <typename TA, typename TW>
 __global__ void __launch_bounds__(GLUE_THREADS)
-depth_average_kernel(const float* __restrict__ hist, long long level_stride, int levels,
-                     const TW* __restrict__ a, const int* __restrict__ rows, float* __restrict__ stream_out,
-                     const TW* __restrict__ nw, TA* __restrict__ norm_out, float eps, int H) {
+depth_average_kernel(const float* hist, long long level_stride, int levels,
+                     const TW* a, const int* rows, float* stream_out,
+                     const TW* nw, TA* norm_out, float eps, int H) {
+  pdl_wait();
+  pdl_launch();
   extern __shared__ float row[];
   __shared__ float red[32];
   const int r = blockIdx.x;
@@ -116,7 +123,7 @@ RLLM_EXPORT int rllm_depth_average(const float* hist, long long level_stride, in
     if (smem > 48 * 1024)                                                                              \
       cudaFuncSetAttribute(depth_average_kernel<TA, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize,  \
                            (int)smem);                                                                 \
-    depth_average_kernel<TA, TW><<<R, GLUE_THREADS, smem, stream>>>(                                   \
+    rllm_launch_pdl(depth_average_kernel<TA, TW>, dim3(R), dim3(GLUE_THREADS), (size_t)(smem), stream,                                    \
         hist, level_stride, levels, (const TW*)a, rows, stream_out, (const TW*)nw, (TA*)norm_out, eps, H); \
   } while (0)
   RLLM_DISPATCH_DTYPE(act_dtype, TA_, RLLM_DISPATCH_DTYPE(w_dtype, TW_, GLUE_LAUNCH(TA_, TW_)));

@@ -15,9 +15,14 @@ __device__ __forceinline__ float sigmoid_f32(float v) { return 1.0f / (1.0f + ex
 
 template <typename TA, typename TW>
 __global__ void __launch_bounds__(MG_THREADS)
-mingru_scan_kernel(const TA* __restrict__ zxg, int stride, const TW* __restrict__ bz, const TW* __restrict__ bx,
-                   float* __restrict__ state, const int* __restrict__ q_start, const int* __restrict__ slots,
-                   int num_slots, TA* __restrict__ out, int W, int* __restrict__ err) {
+mingru_scan_kernel(const TA* zxg, int stride, const TW* bz, const TW* bx,
+                   float* state, const int* q_start, const int* slots,
+                   int num_slots, TA* out, int W, int* err) {
+  // (Every kernel of this file starts with the wait for the kernel ahead of it in the stream and lets the
+  // next one in right after: launches overlap the tails of their predecessors.  The pointer parameters
+  // carry no __restrict__, so that no load is proved independent of that wait and moved above it.)
+  pdl_wait();
+  pdl_launch();
   const int c = blockIdx.x * blockDim.x + threadIdx.x, s = blockIdx.y;
   if (c >= W) return;
   const int slot = slots[s];
@@ -59,10 +64,12 @@ mingru_scan_kernel(const TA* __restrict__ zxg, int stride, const TW* __restrict_
 
 template <typename TA, typename TW>
 __global__ void __launch_bounds__(MG_THREADS)
-mingru_chunk_summary_kernel(const TA* __restrict__ zxg, int stride, const TW* __restrict__ bz,
-                            const TW* __restrict__ bx, const float* __restrict__ state,
-                            const int* __restrict__ q_start, const int* __restrict__ slots, int num_slots,
-                            int max_chunks, float* __restrict__ carry, float* __restrict__ init, int W) {
+mingru_chunk_summary_kernel(const TA* zxg, int stride, const TW* bz,
+                            const TW* bx, const float* state,
+                            const int* q_start, const int* slots, int num_slots,
+                            int max_chunks, float* carry, float* init, int W) {
+  pdl_wait();
+  pdl_launch();
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   const int s = blockIdx.y / max_chunks, k = blockIdx.y % max_chunks;
   if (c >= W) return;
@@ -87,11 +94,13 @@ mingru_chunk_summary_kernel(const TA* __restrict__ zxg, int stride, const TW* __
 
 template <typename TA, typename TW>
 __global__ void __launch_bounds__(MG_THREADS)
-mingru_chunk_scan_kernel(const TA* __restrict__ zxg, int stride, const TW* __restrict__ bz,
-                         const TW* __restrict__ bx, float* __restrict__ state, const int* __restrict__ q_start,
-                         const int* __restrict__ slots, int num_slots, int max_chunks,
-                         const float* __restrict__ carry, const float* __restrict__ init, TA* __restrict__ out,
-                         int W, int* __restrict__ err) {
+mingru_chunk_scan_kernel(const TA* zxg, int stride, const TW* bz,
+                         const TW* bx, float* state, const int* q_start,
+                         const int* slots, int num_slots, int max_chunks,
+                         const float* carry, const float* init, TA* out,
+                         int W, int* err) {
+  pdl_wait();
+  pdl_launch();
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   const int s = blockIdx.y / max_chunks, k = blockIdx.y % max_chunks;
   if (c >= W) return;
@@ -131,9 +140,9 @@ RLLM_EXPORT int rllm_mingru_scan_chunked(const void* zxg, int stride, const void
   float* init = work + (size_t)S * max_chunks * 2 * W;
 #define MG_LAUNCH(TA, TW)                                                                                   \
   do {                                                                                                      \
-    mingru_chunk_summary_kernel<TA, TW><<<grid, MG_THREADS, 0, stream>>>((const TA*)zxg, stride, (const TW*)bz, \
+    rllm_launch_pdl(mingru_chunk_summary_kernel<TA, TW>, dim3(grid), dim3(MG_THREADS), (size_t)(0), stream, (const TA*)zxg, stride, (const TW*)bz, \
         (const TW*)bx, state, q_start, slots, num_slots, max_chunks, carry, init, W);                       \
-    mingru_chunk_scan_kernel<TA, TW><<<grid, MG_THREADS, 0, stream>>>((const TA*)zxg, stride, (const TW*)bz, \
+    rllm_launch_pdl(mingru_chunk_scan_kernel<TA, TW>, dim3(grid), dim3(MG_THREADS), (size_t)(0), stream, (const TA*)zxg, stride, (const TW*)bz, \
         (const TW*)bx, state, q_start, slots, num_slots, max_chunks, carry, init, (TA*)out, W, err);        \
   } while (0)
   RLLM_DISPATCH_DTYPE(act_dtype, TA_, RLLM_DISPATCH_DTYPE(w_dtype, TW_, MG_LAUNCH(TA_, TW_)));
@@ -149,7 +158,7 @@ RLLM_EXPORT int rllm_mingru_scan(const void* zxg, int stride, const void* bz, co
   if (W <= 0 || stride < 3 * W || num_slots <= 0 || S > 65535) return RLLM_E_BADARG;
   dim3 grid((W + MG_THREADS - 1) / MG_THREADS, S);
 #define MG_LAUNCH(TA, TW)                                                                              \
-  mingru_scan_kernel<TA, TW><<<grid, MG_THREADS, 0, stream>>>((const TA*)zxg, stride, (const TW*)bz,   \
+  rllm_launch_pdl(mingru_scan_kernel<TA, TW>, dim3(grid), dim3(MG_THREADS), (size_t)(0), stream, (const TA*)zxg, stride, (const TW*)bz,   \
       (const TW*)bx, state, q_start, slots, num_slots, (TA*)out, W, err)
   RLLM_DISPATCH_DTYPE(act_dtype, TA_, RLLM_DISPATCH_DTYPE(w_dtype, TW_, MG_LAUNCH(TA_, TW_)));
 #undef MG_LAUNCH

@@ -20,8 +20,13 @@
 
 template <typename T>
 __global__ void __launch_bounds__(32 * ROUTE_WARPS)
-moe_route_kernel(const T* __restrict__ h, const T* __restrict__ wr, int* __restrict__ ids,
-                 float* __restrict__ weights, int T_tokens, int H, int E, int top) {
+moe_route_kernel(const T* h, const T* wr, int* ids,
+                 float* weights, int T_tokens, int H, int E, int top) {
+  // (Every kernel of this file starts with the wait for the kernel ahead of it in the stream and lets the
+  // next one in right after: launches overlap the tails of their predecessors.  The pointer parameters
+  // carry no __restrict__, so that no load is proved independent of that wait and moved above it.)
+  pdl_wait();
+  pdl_launch();
   extern __shared__ float zs[];   // [ROUTE_WARPS][E]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int t = blockIdx.x * ROUTE_WARPS + warp;
@@ -70,8 +75,10 @@ moe_route_kernel(const T* __restrict__ h, const T* __restrict__ wr, int* __restr
 
 // the same choice from logits that a matrix product left in float32: z [T, E]
 __global__ void __launch_bounds__(32 * ROUTE_WARPS)
-moe_choose_kernel(const float* __restrict__ logits, int* __restrict__ ids, float* __restrict__ weights,
+moe_choose_kernel(const float* logits, int* ids, float* weights,
                   int T_tokens, int E, int top) {
+  pdl_wait();
+  pdl_launch();
   extern __shared__ float zs[];   // [ROUTE_WARPS][E]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int t = blockIdx.x * ROUTE_WARPS + warp;
@@ -113,7 +120,7 @@ RLLM_EXPORT int rllm_moe_choose(const float* logits, int* ids, float* weights, i
   if (T <= 0) return 0;
   if (E <= 0 || top <= 0 || top > E || E > 2048) return RLLM_E_BADARG;
   const unsigned blocks = (unsigned)((T + ROUTE_WARPS - 1) / ROUTE_WARPS);
-  moe_choose_kernel<<<blocks, 32 * ROUTE_WARPS, (size_t)ROUTE_WARPS * E * sizeof(float), stream>>>(
+  rllm_launch_pdl(moe_choose_kernel, dim3(blocks), dim3(32 * ROUTE_WARPS), (size_t)((size_t)ROUTE_WARPS * E * sizeof(float)), stream, 
       logits, ids, weights, T, E, top);
   RLLM_LAUNCH_CHECK();
   return 0;
@@ -125,7 +132,7 @@ RLLM_EXPORT int rllm_moe_route(const void* h, const void* wr, int* ids, float* w
   if (H <= 0 || E <= 0 || top <= 0 || top > E || E > 2048) return RLLM_E_BADARG;
   const unsigned blocks = (unsigned)((T + ROUTE_WARPS - 1) / ROUTE_WARPS);
   const size_t smem = (size_t)ROUTE_WARPS * E * sizeof(float);
-  RLLM_DISPATCH_DTYPE(dtype, TT, (moe_route_kernel<TT><<<blocks, 32 * ROUTE_WARPS, smem, stream>>>(
+  RLLM_DISPATCH_DTYPE(dtype, TT, (rllm_launch_pdl(moe_route_kernel<TT>, dim3(blocks), dim3(32 * ROUTE_WARPS), (size_t)(smem), stream, 
       (const TT*)h, (const TT*)wr, ids, weights, T, H, E, top)));
   RLLM_LAUNCH_CHECK();
   return 0;
@@ -134,9 +141,11 @@ RLLM_EXPORT int rllm_moe_route(const void* h, const void* wr, int* ids, float* w
 // meta: [0] number of tiles.  offsets [E + 1].  sorted [P]: pair indices by expert.
 // tile_expert, tile_row0 [max_tiles].
 __global__ void __launch_bounds__(1024)
-moe_sort_kernel(const int* __restrict__ ids, int P, int E, int bm, int* __restrict__ offsets,
-                int* __restrict__ sorted, int* __restrict__ tile_expert, int* __restrict__ tile_row0,
-                int* __restrict__ meta) {
+moe_sort_kernel(const int* ids, int P, int E, int bm, int* offsets,
+                int* sorted, int* tile_expert, int* tile_row0,
+                int* meta) {
+  pdl_wait();
+  pdl_launch();
   extern __shared__ int sh[];      // counts [E], start [E + 1], tile_start [E + 1], cursor [E]
   int* cnt = sh;
   int* start = cnt + E;
@@ -176,7 +185,7 @@ RLLM_EXPORT int rllm_moe_sort(const int* ids, int P, int E, int bm, int* offsets
   if (P <= 0) return 0;
   if (E <= 0 || E > 2048 || (bm != 16 && bm != 64)) return RLLM_E_BADARG;
   const size_t smem = (size_t)(4 * E + 2) * sizeof(int);
-  moe_sort_kernel<<<1, 1024, smem, stream>>>(ids, P, E, bm, offsets, sorted, tile_expert, tile_row0, meta);
+  rllm_launch_pdl(moe_sort_kernel, dim3(1), dim3(1024), (size_t)(smem), stream, ids, P, E, bm, offsets, sorted, tile_expert, tile_row0, meta);
   RLLM_LAUNCH_CHECK();
   return 0;
 }
@@ -184,10 +193,12 @@ RLLM_EXPORT int rllm_moe_sort(const int* ids, int P, int E, int bm, int* offsets
 // y[row, n] = act(h[token(row)] . Wg[e][n], h[token(row)] . Wu[e][n]);  w: [E, 2 F, H], gate rows then up rows
 template <typename T, int BM>
 __global__ void __launch_bounds__(TG_THREADS)
-moe_gate_up_kernel(const T* __restrict__ h, const T* __restrict__ w, T* __restrict__ y,
-                   const int* __restrict__ offsets, const int* __restrict__ sorted,
-                   const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
-                   const int* __restrict__ meta, int H, int F, int top, float limit, float alpha) {
+moe_gate_up_kernel(const T* h, const T* w, T* y,
+                   const int* offsets, const int* sorted,
+                   const int* tile_expert, const int* tile_row0,
+                   const int* meta, int H, int F, int top, float limit, float alpha) {
+  pdl_wait();
+  pdl_launch();
   __shared__ TileGemmSmem<BM> sm;
   const int tile = blockIdx.y;
   if (tile >= meta[0]) return;
@@ -220,10 +231,12 @@ moe_gate_up_kernel(const T* __restrict__ h, const T* __restrict__ w, T* __restri
 // out[pair(row), n] = y[row] . Wd[e][n];  w: [E, H, F]
 template <typename T, int BM>
 __global__ void __launch_bounds__(TG_THREADS)
-moe_down_kernel(const T* __restrict__ y, const T* __restrict__ w, T* __restrict__ out,
-                const int* __restrict__ offsets, const int* __restrict__ sorted,
-                const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
-                const int* __restrict__ meta, int H, int F) {
+moe_down_kernel(const T* y, const T* w, T* out,
+                const int* offsets, const int* sorted,
+                const int* tile_expert, const int* tile_row0,
+                const int* meta, int H, int F) {
+  pdl_wait();
+  pdl_launch();
   __shared__ TileGemmSmem<BM> sm;
   const int tile = blockIdx.y;
   if (tile >= meta[0]) return;
@@ -253,11 +266,13 @@ moe_down_kernel(const T* __restrict__ y, const T* __restrict__ w, T* __restrict_
 // the same two kernels on the tensor cores (bfloat16)
 template <int BM>
 __global__ void __launch_bounds__(TGM_THREADS)
-moe_gate_up_mma_kernel(const bf16* __restrict__ h, const bf16* __restrict__ w, bf16* __restrict__ y,
-                       const int* __restrict__ offsets, const int* __restrict__ sorted,
-                       const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
-                       const int* __restrict__ meta, int H, int F, int top, float limit, float alpha) {
-  __shared__ __align__(16) MmaTileSmem<BM, 2> sm;
+moe_gate_up_mma_kernel(const bf16* h, const bf16* w, bf16* y,
+                       const int* offsets, const int* sorted,
+                       const int* tile_expert, const int* tile_row0,
+                       const int* meta, int H, int F, int top, float limit, float alpha) {
+  pdl_wait();
+  pdl_launch();
+  MmaTileSmem<BM, 2>& sm = tgm_smem<BM, 2>();
   const int tile = blockIdx.y;
   if (tile >= meta[0]) return;
   const int e = tile_expert[tile], r0 = tile_row0[tile], rend = offsets[e + 1];
@@ -287,11 +302,13 @@ moe_gate_up_mma_kernel(const bf16* __restrict__ h, const bf16* __restrict__ w, b
 
 template <int BM>
 __global__ void __launch_bounds__(TGM_THREADS)
-moe_down_mma_kernel(const bf16* __restrict__ y, const bf16* __restrict__ w, bf16* __restrict__ out,
-                    const int* __restrict__ offsets, const int* __restrict__ sorted,
-                    const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
-                    const int* __restrict__ meta, int H, int F) {
-  __shared__ __align__(16) MmaTileSmem<BM, 1> sm;
+moe_down_mma_kernel(const bf16* y, const bf16* w, bf16* out,
+                    const int* offsets, const int* sorted,
+                    const int* tile_expert, const int* tile_row0,
+                    const int* meta, int H, int F) {
+  pdl_wait();
+  pdl_launch();
+  MmaTileSmem<BM, 1>& sm = tgm_smem<BM, 1>();
   const int tile = blockIdx.y;
   if (tile >= meta[0]) return;
   const int e = tile_expert[tile], r0 = tile_row0[tile], rend = offsets[e + 1];
@@ -319,8 +336,10 @@ moe_down_mma_kernel(const bf16* __restrict__ y, const bf16* __restrict__ w, bf16
 
 // out[t, :] = sum_k c[t, k] y[t * K + k, :], the k terms in order
 template <typename T>
-__global__ void weighted_slot_sum_kernel(const T* __restrict__ y, const float* __restrict__ c, T* __restrict__ out,
+__global__ void weighted_slot_sum_kernel(const T* y, const float* c, T* out,
                                          int slots, int H, long long total) {
+  pdl_wait();
+  pdl_launch();
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   const long long t = idx / H;
@@ -336,7 +355,7 @@ RLLM_EXPORT int rllm_weighted_slot_sum(const void* y, const float* c, void* out,
   if (total <= 0) return 0;
   if (slots <= 0) return RLLM_E_BADARG;
   const unsigned blocks = (unsigned)((total + 255) / 256);
-  RLLM_DISPATCH_DTYPE(dtype, TT, (weighted_slot_sum_kernel<TT><<<blocks, 256, 0, stream>>>(
+  RLLM_DISPATCH_DTYPE(dtype, TT, (rllm_launch_pdl(weighted_slot_sum_kernel<TT>, dim3(blocks), dim3(256), (size_t)(0), stream, 
       (const TT*)y, c, (TT*)out, slots, H, total)));
   RLLM_LAUNCH_CHECK();
   return 0;
@@ -355,9 +374,11 @@ RLLM_EXPORT int rllm_moe_experts(const void* h, const void* w_gate_up, const voi
   if (dtype == RLLM_DT_BF16 && aligned && !tgm_disabled()) {
 #define MOE_MMA(BM_)                                                                                         \
   do {                                                                                                       \
-    moe_gate_up_mma_kernel<BM_><<<g1, TGM_THREADS, 0, stream>>>((const bf16*)h, (const bf16*)w_gate_up,      \
+    tgm_allow_smem<decltype(&moe_gate_up_mma_kernel<BM_>), BM_, 2>(moe_gate_up_mma_kernel<BM_>);             \
+    rllm_launch_pdl(moe_gate_up_mma_kernel<BM_>, dim3(g1), dim3(TGM_THREADS), (size_t)(sizeof(MmaTileSmem<BM_, 2>)), stream, (const bf16*)h, (const bf16*)w_gate_up,      \
         (bf16*)y, offsets, sorted, tile_expert, tile_row0, meta, H, F, top, limit, alpha);                   \
-    moe_down_mma_kernel<BM_><<<g2, TGM_THREADS, 0, stream>>>((const bf16*)y, (const bf16*)w_down, (bf16*)out, \
+    tgm_allow_smem<decltype(&moe_down_mma_kernel<BM_>), BM_, 1>(moe_down_mma_kernel<BM_>);                   \
+    rllm_launch_pdl(moe_down_mma_kernel<BM_>, dim3(g2), dim3(TGM_THREADS), (size_t)(sizeof(MmaTileSmem<BM_, 1>)), stream, (const bf16*)y, (const bf16*)w_down, (bf16*)out, \
         offsets, sorted, tile_expert, tile_row0, meta, H, F);                                                \
   } while (0)
     if (bm == 16) MOE_MMA(16); else MOE_MMA(64);
@@ -367,9 +388,9 @@ RLLM_EXPORT int rllm_moe_experts(const void* h, const void* w_gate_up, const voi
   }
 #define MOE_LAUNCH(T_, BM_)                                                                                  \
   do {                                                                                                       \
-    moe_gate_up_kernel<T_, BM_><<<g1, TG_THREADS, 0, stream>>>((const T_*)h, (const T_*)w_gate_up, (T_*)y,    \
+    rllm_launch_pdl(moe_gate_up_kernel<T_, BM_>, dim3(g1), dim3(TG_THREADS), (size_t)(0), stream, (const T_*)h, (const T_*)w_gate_up, (T_*)y,    \
         offsets, sorted, tile_expert, tile_row0, meta, H, F, top, limit, alpha);                             \
-    moe_down_kernel<T_, BM_><<<g2, TG_THREADS, 0, stream>>>((const T_*)y, (const T_*)w_down, (T_*)out, offsets, \
+    rllm_launch_pdl(moe_down_kernel<T_, BM_>, dim3(g2), dim3(TG_THREADS), (size_t)(0), stream, (const T_*)y, (const T_*)w_down, (T_*)out, offsets, \
         sorted, tile_expert, tile_row0, meta, H, F);                                                         \
   } while (0)
   RLLM_DISPATCH_DTYPE(dtype, TT, { if (bm == 16) MOE_LAUNCH(TT, 16); else MOE_LAUNCH(TT, 64); });

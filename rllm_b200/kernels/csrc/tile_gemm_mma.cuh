@@ -1,7 +1,8 @@
 // The tile of tile_gemm.cuh on the tensor cores, for bfloat16: C = A . B^T with A's rows
 // given as pointers (gathered rows, null = zeros) and one or two B matrices [N, K] that
 // share the A tile (a gate and an up projection, say).  128 threads, a tile of BM x 64
-// outputs per B matrix, k in steps of 32 through a cp.async double buffer,
+// outputs per B matrix, k in steps of 32 through a cp.async ring of four stages (dynamic
+// shared memory: the caller passes sizeof(MmaTileSmem<BM, NB>) at the launch),
 // mma.sync m16n8k16 with float32 accumulators.  An output's k terms are added in the
 // same order whatever else is in the tile, and BM = 16 and BM = 64 give the same bits.
 // Needs K % 8 == 0 and 16-byte aligned rows of A and B.
@@ -13,12 +14,26 @@
 #define TGM_BK 32
 #define TGM_LD (TGM_BK + 8)      // bf16 elements per shared row: 80 bytes, conflict-free fragment loads
 
+#define TGM_STAGES 4
+
 template <int BM, int NB>
 struct MmaTileSmem {
-  bf16 A[2][BM][TGM_LD];
-  bf16 B[2][NB * TGM_BN][TGM_LD];
+  bf16 A[TGM_STAGES][BM][TGM_LD];
+  bf16 B[TGM_STAGES][NB * TGM_BN][TGM_LD];
   const void* rows[BM];
 };
+
+// the kernel's dynamic shared memory as the tile's buffers
+template <int BM, int NB>
+__device__ __forceinline__ MmaTileSmem<BM, NB>& tgm_smem() {
+  extern __shared__ __align__(16) unsigned char tgm_raw[];
+  return *reinterpret_cast<MmaTileSmem<BM, NB>*>(tgm_raw);
+}
+template <typename K, int BM, int NB>
+static inline void tgm_allow_smem(K kernel) {
+  if (sizeof(MmaTileSmem<BM, NB>) > 48 * 1024)
+    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(MmaTileSmem<BM, NB>));
+}
 
 __device__ __forceinline__ void tgm_cp16(void* smem_dst, const void* src, bool valid) {
   const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
@@ -26,12 +41,18 @@ __device__ __forceinline__ void tgm_cp16(void* smem_dst, const void* src, bool v
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
 }
 __device__ __forceinline__ void tgm_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void tgm_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void tgm_wait_ring() { asm volatile("cp.async.wait_group %0;" ::"n"(TGM_STAGES - 2) : "memory"); }
 
 __device__ __forceinline__ void tgm_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ void tgm_ldmatrix4(uint32_t (&r)[4], const void* smem_row) {
+  const unsigned addr = (unsigned)__cvta_generic_to_shared(smem_row);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
 }
 
 // NT: n-tiles of 8 columns a warp owns (BM 64: 8, all 64 columns of its 16 rows; BM 16: 2)
@@ -44,7 +65,7 @@ __device__ __forceinline__ void tgm_load_stage(MmaTileSmem<BM, NB>& sm, int st, 
   for (int c = tid; c < BM * 4; c += TGM_THREADS) {
     const int r = c >> 2, kc = (c & 3) * 8;
     const bf16* p = (const bf16*)sm.rows[r];
-    const bool ok = p != nullptr && k0 + kc < K;
+    const bool ok = p != nullptr && k0 + kc < K && k0 < K;
     tgm_cp16(&sm.A[st][r][kc], ok ? (const void*)(p + k0 + kc) : (const void*)B[0], ok);
   }
 #pragma unroll
@@ -55,7 +76,6 @@ __device__ __forceinline__ void tgm_load_stage(MmaTileSmem<BM, NB>& sm, int st, 
       tgm_cp16(&sm.B[st][b * TGM_BN + n][kc], ok ? (const void*)(B[b] + (long long)(n0 + n) * ldb + k0 + kc) : (const void*)B[0], ok);
     }
   }
-  tgm_commit();
 }
 
 // acc[b][nt][4]: fragment of B matrix b, n-tile nt.  Element i of a fragment is output
@@ -66,7 +86,6 @@ __device__ __forceinline__ void tile_gemm_mma(MmaTileSmem<BM, NB>& sm, const bf1
                                               int n0, int N, int K, float (&acc)[NB][TgmShape<BM>::NT][4]) {
   constexpr int NT = TgmShape<BM>::NT;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int g = lane >> 2, t = lane & 3;
   const int row0 = (BM == 64) ? warp * 16 : 0;
   const int col0 = (BM == 64) ? 0 : warp * 16;
 #pragma unroll
@@ -76,25 +95,33 @@ __device__ __forceinline__ void tile_gemm_mma(MmaTileSmem<BM, NB>& sm, const bf1
 #pragma unroll
       for (int i = 0; i < 4; ++i) acc[b][nt][i] = 0.f;
   const int steps = (K + TGM_BK - 1) / TGM_BK;
-  tgm_load_stage<BM, NB>(sm, 0, B, ldb, n0, N, K, 0);
+  // a group is committed for every step of the ring, also an empty one, so that "all but the last
+  // TGM_STAGES - 2 groups have landed" always means: the stage about to be read has
+#pragma unroll
+  for (int s = 0; s < TGM_STAGES - 1; ++s) {
+    if (s < steps) tgm_load_stage<BM, NB>(sm, s, B, ldb, n0, N, K, s * TGM_BK);
+    tgm_commit();
+  }
   for (int s = 0; s < steps; ++s) {
-    const int st = s & 1;
-    tgm_wait_all();
-    __syncthreads();
-    if (s + 1 < steps) tgm_load_stage<BM, NB>(sm, st ^ 1, B, ldb, n0, N, K, (s + 1) * TGM_BK);
+    const int st = s % TGM_STAGES;
+    tgm_wait_ring();
+    __syncthreads();               // stage st has landed for everyone, and everyone has left step s - 1
+    if (s + TGM_STAGES - 1 < steps)
+      tgm_load_stage<BM, NB>(sm, (s + TGM_STAGES - 1) % TGM_STAGES, B, ldb, n0, N, K, (s + TGM_STAGES - 1) * TGM_BK);
+    tgm_commit();
 #pragma unroll
     for (int kk = 0; kk < TGM_BK; kk += 16) {
+      // fragments by ldmatrix: A's 16 x 16 in one, B's 8 x 16 of two n-tiles in one
       uint32_t a[4];
-      a[0] = *(const uint32_t*)&sm.A[st][row0 + g][kk + 2 * t];
-      a[1] = *(const uint32_t*)&sm.A[st][row0 + g + 8][kk + 2 * t];
-      a[2] = *(const uint32_t*)&sm.A[st][row0 + g][kk + 2 * t + 8];
-      a[3] = *(const uint32_t*)&sm.A[st][row0 + g + 8][kk + 2 * t + 8];
+      tgm_ldmatrix4(a, &sm.A[st][row0 + (lane & 15)][kk + (lane >> 4) * 8]);
 #pragma unroll
       for (int b = 0; b < NB; ++b)
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-          const bf16* br = &sm.B[st][b * TGM_BN + col0 + nt * 8 + g][kk + 2 * t];
-          tgm_mma(acc[b][nt], a, *(const uint32_t*)br, *(const uint32_t*)(br + 8));
+        for (int nt = 0; nt < NT; nt += 2) {
+          uint32_t bb[4];
+          tgm_ldmatrix4(bb, &sm.B[st][b * TGM_BN + col0 + nt * 8 + (lane & 7) + ((lane >> 4) & 1) * 8][kk + ((lane >> 3) & 1) * 8]);
+          tgm_mma(acc[b][nt], a, bb[0], bb[1]);
+          tgm_mma(acc[b][nt + 1], a, bb[2], bb[3]);
         }
     }
   }

@@ -798,7 +798,7 @@ def latent_attention_simt(q: torch.Tensor, out: torch.Tensor, cache: torch.Tenso
 
 LATENT_SPLIT_MAX_TILES = 64      # at most this many row tiles in a launch (they fill less than half the GPU) ...
 LATENT_SPLIT_MIN_KEYS = 1024     # ... and at least this many keys to walk: the keys are cut into splits too
-LATENT_SPLIT_KEYS = 256          # keys a split (a multiple of 32, at absolute positions)
+LATENT_SPLIT_KEYS = 128          # keys a split (a multiple of 64, at absolute positions)
 
 
 def latent_attention_mma_takes(dtype: torch.dtype, dk: int, dv: int) -> bool:
@@ -815,14 +815,14 @@ def latent_attention_mma(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor
     """The same attention as ``latent_attention_simt`` on the tensor cores, for bfloat16.  Sequence s owns
     tokens q_start[s] .. q_start[s+1], the last of them at position seq_lens[s] - 1; ``max_q_len``: the most
     tokens a sequence brings (sizes the grid).  ``max_seq_len`` (an upper bound of seq_lens, 0: unknown): with
-    few rows and long sequences the keys are also cut into splits of 256 that run side by side."""
+    few rows and long sequences the keys are also cut into splits of 128 that run side by side."""
     lib = build.load_library("latent_attention_mma")
     split_tiles, nsplit, work = 0, 1, None
     row_tiles = num_seqs * -(-(max_q_len * heads) // 64)
     keys = min(max_seq_len, window + max_q_len) if window else max_seq_len
     if row_tiles <= LATENT_SPLIT_MAX_TILES and keys >= LATENT_SPLIT_MIN_KEYS:
-        split_tiles = LATENT_SPLIT_KEYS // 32
-        nsplit = -(-(-(-max_seq_len // 32)) // split_tiles)
+        split_tiles = LATENT_SPLIT_KEYS                     # in keys: a multiple of every key tile
+        nsplit = -(-max_seq_len // LATENT_SPLIT_KEYS)
         lib.rllm_latent_attention_mma_work.restype = c_longlong
         n = int(lib.rllm_latent_attention_mma_work(c_int(num_seqs), c_int(max_q_len), c_int(heads), c_int(dv),
                                                    c_int(nsplit)))

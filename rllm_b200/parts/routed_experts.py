@@ -31,9 +31,6 @@ from .registry import register_part
 from .spec import PartSpec, TensorSpec
 
 
-ROUTE_FUSED_ROWS = 64      # up to here one kernel computes logits, softmax and choice of a token
-
-
 @register_part("feed_forward", "routed_experts")
 class RoutedExperts(FeedForward):
     graph_safe = True
@@ -75,11 +72,10 @@ class RoutedExperts(FeedForward):
         self.w_down = torch.stack([tensors[self._expert("down", e)] for e in range(self.experts)]).contiguous()
 
     def forward_slots(self, x: torch.Tensor):
-        if x.shape[0] > ROUTE_FUSED_ROWS:
-            # many rows: the logits are one matrix product with a float32 result, the choice a small kernel
-            ids, scores = ops.moe_choose(linear(x, self.w_router, out_dtype=torch.float32), self.top)
-        else:
-            ids, scores = ops.moe_route(x, self.w_router, self.top)
+        # the logits are one matrix product with a float32 result (float32 accumulation from the first term
+        # on), softmax and choice a small kernel (``ops.moe_route`` is the same in one kernel, a warp a token:
+        # the form the two are checked against)
+        ids, scores = ops.moe_choose(linear(x, self.w_router, out_dtype=torch.float32), self.top)
         return ops.moe_experts(x, ids, self.w_gate_up, self.w_down, self.limit, self.alpha), scores
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
