@@ -61,6 +61,7 @@ mingru_scan_kernel(const TA* zxg, int stride, const TW* bz, const TW* bx,
 // the chunks before it (in order) and walks its tokens as the plain kernel does.  Results differ from the
 // plain kernel's by rounding only, and do not depend on what else is in the batch.
 #define MG_CHUNK 64
+#define MG_BATCH 8
 
 template <typename TA, typename TW>
 __global__ void __launch_bounds__(MG_THREADS)
@@ -80,12 +81,22 @@ mingru_chunk_summary_kernel(const TA* zxg, int stride, const TW* bz,
   if (k == 0) init[(size_t)s * W + c] = state[(size_t)slot * W + c];
   const float biasz = to_f32(bz[c]), biasx = to_f32(bx[c]);
   float A = 1.f, B = 0.f;
-  for (int t = t0; t < t1; ++t) {
-    const TA* r = zxg + (size_t)t * stride + c;
-    const float z = sigmoid_f32(to_f32(r[0]) + biasz), u = to_f32(r[W]) + biasx;
-    const float cand = (u >= 0.f) ? u + 0.5f : sigmoid_f32(u);
-    A *= 1.0f - z;
-    B = fmaf(1.0f - z, B, z * cand);
+  for (int tb = t0; tb < t1; tb += MG_BATCH) {        // a batch of tokens' values are fetched before the chain runs
+    float az[MG_BATCH], ax[MG_BATCH];
+#pragma unroll
+    for (int i = 0; i < MG_BATCH; ++i) {
+      const TA* r = zxg + (size_t)min(tb + i, t1 - 1) * stride + c;
+      az[i] = to_f32(r[0]); ax[i] = to_f32(r[W]);
+    }
+#pragma unroll
+    for (int i = 0; i < MG_BATCH; ++i) {
+      if (tb + i < t1) {
+        const float z = sigmoid_f32(az[i] + biasz), u = ax[i] + biasx;
+        const float cand = (u >= 0.f) ? u + 0.5f : sigmoid_f32(u);
+        A *= 1.0f - z;
+        B = fmaf(1.0f - z, B, z * cand);
+      }
+    }
   }
   float* o = carry + ((size_t)blockIdx.y * 2) * W + c;
   o[0] = A;
@@ -117,12 +128,22 @@ mingru_chunk_scan_kernel(const TA* zxg, int stride, const TW* bz,
     S = fmaf(p[0], S, p[W]);
   }
   const float biasz = to_f32(bz[c]), biasx = to_f32(bx[c]);
-  for (int t = t0; t < t1; ++t) {
-    const TA* r = zxg + (size_t)t * stride + c;
-    const float z = sigmoid_f32(to_f32(r[0]) + biasz), u = to_f32(r[W]) + biasx, g = to_f32(r[2 * W]);
-    const float cand = (u >= 0.f) ? u + 0.5f : sigmoid_f32(u);
-    S = fmaf(1.0f - z, S, z * cand);
-    out[(size_t)t * W + c] = from_f32<TA>(S * (g * sigmoid_f32(g)));
+  for (int tb = t0; tb < t1; tb += MG_BATCH) {
+    float az[MG_BATCH], ax[MG_BATCH], ag[MG_BATCH];
+#pragma unroll
+    for (int i = 0; i < MG_BATCH; ++i) {
+      const TA* r = zxg + (size_t)min(tb + i, t1 - 1) * stride + c;
+      az[i] = to_f32(r[0]); ax[i] = to_f32(r[W]); ag[i] = to_f32(r[2 * W]);
+    }
+#pragma unroll
+    for (int i = 0; i < MG_BATCH; ++i) {
+      if (tb + i < t1) {
+        const float z = sigmoid_f32(az[i] + biasz), u = ax[i] + biasx;
+        const float cand = (u >= 0.f) ? u + 0.5f : sigmoid_f32(u);
+        S = fmaf(1.0f - z, S, z * cand);
+        out[(size_t)(tb + i) * W + c] = from_f32<TA>(S * (ag[i] * sigmoid_f32(ag[i])));
+      }
+    }
   }
   if (t1 == q_start[s + 1]) state[(size_t)slot * W + c] = S;
 }

@@ -4,6 +4,9 @@
     python -m rllm_b200.kernels.microbench attention_prefill --tokens 2048 [--impl tcgen05]
     python -m rllm_b200.kernels.microbench gemm_small_m --rows 8 [--variant residual|rstd]
     python -m rllm_b200.kernels.microbench gemm_tcgen05 --rows 2048
+    python -m rllm_b200.kernels.microbench latent_attention --tokens 2048 --heads 16 --kv-rank 512 --rot-dim 64
+    python -m rllm_b200.kernels.microbench latent_attention --batch 8 --context 4096 --tokens 1 ...
+    python -m rllm_b200.kernels.microbench routed_experts --rows 2048 --experts 32 --top 4 --intermediate 1024
 
 Sizes default to the Llama-3.2-1B shape (32 heads, 8 kv heads, head 64, hidden
 2048, intermediate 8192).  Times are CUDA-event times over ``--iters`` launches
@@ -108,6 +111,52 @@ def attention_prefill(args) -> None:
         print(f"error word {int(err.item())}", file=sys.stderr)
 
 
+def latent_attention(args) -> None:
+    """--tokens > 1: one prompt of that many tokens; --tokens 1: --batch sequences of --context cached rows."""
+    heads, dv, dk, page = args.heads, args.kv_rank, args.kv_rank + args.rot_dim, args.page
+    if args.tokens > 1:
+        S, nq, ctx = 1, args.tokens, args.tokens
+    else:
+        S, nq, ctx = args.batch, 1, args.context
+    per = -(-ctx // page)
+    cache = torch.randn(S * per + 4, 1, page, dk, device=DEV).bfloat16()
+    table = torch.randperm(S * per, device=DEV).int().view(S, per).contiguous()
+    T = S * nq
+    q = torch.randn(T, heads * dk, device=DEV).bfloat16()
+    out = torch.empty(T, heads * dv, device=DEV, dtype=torch.bfloat16)
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    q_start = torch.arange(0, T + 1, nq, dtype=torch.int32, device=DEV)
+    seq_lens = torch.full((S,), ctx, dtype=torch.int32, device=DEV)
+    scale = 1 / math.sqrt(dk)
+
+    def run(i):
+        ops.latent_attention_mma(q, out, cache, table, q_start, seq_lens, S, nq, heads, dk, dv, args.window, scale, None,
+                                 err, max_seq_len=ctx)
+    us = time_us(run, args.iters)
+    vis = sum(min(p + 1, args.window or p + 1) for p in range(ctx - nq, ctx)) * S
+    flops = 2 * (dk + dv) * heads * vis
+    gb = 2 * S * min(ctx, (args.window or ctx) + nq) * dk / 1e9
+    print(f"latent_attention tokens {T} context {ctx} heads {heads} rows of {dk} (values {dv}): {us:.1f} us, "
+          f"{flops / us / 1e6:.1f} TFLOP/s, rows read once {gb / us * 1e6:.0f} GB/s")
+    if int(err.item()):
+        print(f"error word {int(err.item())}", file=sys.stderr)
+
+
+def routed_experts(args) -> None:
+    T, H, F, E, top = args.rows, args.hidden, args.intermediate, args.experts, args.top
+    x = torch.randn(T, H, device=DEV).bfloat16()
+    wgu = (torch.randn(E, 2 * F, H, device=DEV) * 0.02).bfloat16()
+    wd = (torch.randn(E, H, F, device=DEV) * 0.02).bfloat16()
+    ids = torch.stack([torch.randperm(E, device=DEV)[:top] for _ in range(T)]).int().contiguous()
+
+    def run(i):
+        ops.moe_experts(x, ids, wgu, wd, 7.0, 1.702)
+    us = time_us(run, args.iters)
+    used = min(E, T * top)
+    print(f"routed_experts rows {T} x top {top} of {E} experts ({H} -> {F} -> {H}): {us:.1f} us, "
+          f"{2 * 3 * H * F * T * top / us / 1e6:.1f} TFLOP/s, touched weights once {used * 3 * H * F * 2 / us / 1e3:.0f} GB/s")
+
+
 def _shapes(args):
     H, I = args.hidden, args.intermediate
     qkv = (args.heads + 2 * args.kv_heads) * args.head_dim
@@ -166,7 +215,8 @@ def gemm_tcgen05(args) -> None:
 
 def main(argv=None) -> int:
     p = argparse.ArgumentParser(prog="python -m rllm_b200.kernels.microbench", description=__doc__.split("\n\n")[0])
-    p.add_argument("kernel", choices=["attention_decode", "attention_prefill", "gemm_small_m", "gemm_tcgen05"])
+    p.add_argument("kernel", choices=["attention_decode", "attention_prefill", "gemm_small_m", "gemm_tcgen05",
+                                      "latent_attention", "routed_experts"])
     p.add_argument("--batch", type=int, default=8)
     p.add_argument("--context", type=int, default=4096)
     p.add_argument("--tokens", type=int, default=2048)
@@ -178,6 +228,11 @@ def main(argv=None) -> int:
     p.add_argument("--hidden", type=int, default=2048)
     p.add_argument("--intermediate", type=int, default=8192)
     p.add_argument("--page", type=int, default=16)
+    p.add_argument("--kv-rank", type=int, default=512, help="latent_attention: values of a cached row")
+    p.add_argument("--rot-dim", type=int, default=64, help="latent_attention: the rows' rotated key part")
+    p.add_argument("--window", type=int, default=0, help="latent_attention: keys a query sees (0: all)")
+    p.add_argument("--experts", type=int, default=32)
+    p.add_argument("--top", type=int, default=4)
     p.add_argument("--variant", choices=["plain", "residual", "rstd"], default="plain",
                    help="gemm_small_m: which epilogue / operand form")
     p.add_argument("--only", choices=["qkv", "o_proj", "gate_up", "down"], default=None,
@@ -189,7 +244,8 @@ def main(argv=None) -> int:
         print("microbench needs a CUDA device", file=sys.stderr)
         return 1
     {"attention_decode": attention_decode, "attention_prefill": attention_prefill,
-     "gemm_small_m": gemm_small_m, "gemm_tcgen05": gemm_tcgen05}[args.kernel](args)
+     "gemm_small_m": gemm_small_m, "gemm_tcgen05": gemm_tcgen05, "latent_attention": latent_attention,
+     "routed_experts": routed_experts}[args.kernel](args)
     return 0
 
 

@@ -732,7 +732,7 @@ def latent_prep(a: torch.Tensor, q_rank: int, kv_rank: int, rot: int, rot_dims: 
     assert a.stride(1) == 1 and cq.shape == (T, q_rank) and cq.dtype is a.dtype
     _contig(cq, "cq")
     if write:
-        assert a.shape[1] == q_rank + kv_rank + rot and cache.dtype is a.dtype and cache.shape[3] == kv_rank + rot
+        assert a.shape[1] >= q_rank + kv_rank + rot and cache.dtype is a.dtype and cache.shape[3] == kv_rank + rot
         assert cache.shape[1] == 1 and wkv is not None and wkv.dtype is wq.dtype
         _contig(cache, "cache"); _contig(block_table, "block_table")
         if rot_dims:

@@ -196,6 +196,12 @@ class Mixer(Part):
     def cache_need(self):
         return None
 
+    def stack_input(self, weight: torch.Tensor) -> bool:
+        """A block may hand a mixer one more weight [rows, H] that reads the mixer's own input: a mixer whose
+        first step is a matrix product over stacked weights appends it there and returns True; its
+        ``forward(..., side=True)`` then returns (result, that product's extra columns [T, rows], a view)."""
+        return False
+
     def forward(self, x: torch.Tensor, ctx: StepContext, cache) -> torch.Tensor:
         raise NotImplementedError
 

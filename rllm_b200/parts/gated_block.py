@@ -13,7 +13,9 @@ learned d.  The results X_j are float32 and kept for the whole step
 (``ctx.extras["depth_history"]``, made by the model); gate, norms, adds and the
 weighted sum are float32 arithmetic.  The gate's sigmoid, the norm of the gated
 result, the add and the norm that reads the stream next are one kernel; so are the
-weighted sum over the depth and the next layer's first norm.
+weighted sum over the depth and the next layer's first norm.  The mixer's gate product
+joins the mixer's own first product where the mixer stacks its input weights
+(``Mixer.stack_input``).
 
 norms: four (norm_0 .. norm_3).  params: hidden_size, depth_levels (0: none),
 tensor_names (keys "gate1", "gate1_bias", "gate2", "gate2_bias", "depth": names
@@ -54,6 +56,7 @@ class SandwichGatedBlock(Part):
             raise ValueError(f"a sandwich_gated spec names its tensors: tensor_names with the keys {_KEYS}")
         self.names = {k: prefix + str(v) for k, v in names.items()}
         self.w_g1 = self.b_g1 = self.w_g2 = self.b_g2 = self.depth = None
+        self._stacked: Optional[bool] = None
 
     @property
     def graph_safe(self) -> bool:
@@ -76,6 +79,7 @@ class SandwichGatedBlock(Part):
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
         n = self.names
         self.w_g1, self.b_g1 = tensors[n["gate1"]], tensors[n["gate1_bias"]].contiguous()
+        self._stacked = None
         if self.ffn is not None:
             self.w_g2, self.b_g2 = tensors[n["gate2"]], tensors[n["gate2_bias"]].contiguous()
         if self.depth_levels:
@@ -98,8 +102,16 @@ class SandwichGatedBlock(Part):
             x = h
         nxt_w = getattr(next_norm, "weight", None) if next_norm is not None and hasattr(next_norm, "eps") else None
         nxt_eps = float(next_norm.eps) if nxt_w is not None else 0.0
-        m = self.mixer.forward(a, ctx, cache)
-        g = linear(a, self.w_g1)
+        if self._stacked is None:
+            # the mixer's gate reads the mixer's input: one product with the mixer's own first one, if it can
+            self._stacked = bool(self.mixer.stack_input(self.w_g1))
+            if self._stacked:
+                self.w_g1 = None
+        if self._stacked:
+            m, g = self.mixer.forward(a, ctx, cache, side=True)
+        else:
+            m = self.mixer.forward(a, ctx, cache)
+            g = linear(a, self.w_g1)
         last = self.ffn is None
         direct = nxt_w if (last and not self.depth_levels) else None
         b = ops.gated_postnorm_add(h, x, m, g, self.b_g1, n1.weight, n1.eps,

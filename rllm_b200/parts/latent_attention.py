@@ -105,7 +105,14 @@ class LatentAttention(Mixer):
     def cache_need(self):
         return KVPagesNeed(1, self.kv_rank + self.rot, self.window, values=False)
 
-    def forward(self, x, ctx: StepContext, cache: KVCacheView):
+    def _down_rows(self) -> int:
+        return self.q_rank + (0 if self.shares_kv else self.kv_rank + self.rot)
+
+    def stack_input(self, weight: torch.Tensor) -> bool:
+        self.w_down = torch.cat([self.w_down[: self._down_rows()], weight], dim=0).contiguous()
+        return True
+
+    def forward(self, x, ctx: StepContext, cache: KVCacheView, side: bool = False):
         T, H = x.shape[0], self.heads
         dk = self.kv_rank + self.rot
         inv_freq = self.position.table(x.device) if self.rot_dims else None
@@ -131,4 +138,5 @@ class LatentAttention(Mixer):
                                       int(self.window or 0), self.scale, self.sink, ctx.err)
         ov = torch.empty((T, H * self.vdim), dtype=x.dtype, device=x.device)
         ops.head_gemm(o.view(T, H, self.kv_rank), self.w_uv, ov.view(T, H, self.vdim), b_kn=False)
-        return linear(ov, self.w_o)
+        y = linear(ov, self.w_o)
+        return (y, a[:, self._down_rows():]) if side else y

@@ -62,9 +62,14 @@ class MinGRU(Mixer):
     def cache_need(self):
         return StateNeed((self.width,))
 
-    def forward(self, x, ctx: StepContext, cache: StateCacheView):
-        a = linear(x, self.w_in)                                   # [T, 3 width]: z | x | g
+    def stack_input(self, weight: torch.Tensor) -> bool:
+        self.w_in = torch.cat([self.w_in[: 3 * self.width], weight], dim=0).contiguous()
+        return True
+
+    def forward(self, x, ctx: StepContext, cache: StateCacheView, side: bool = False):
+        a = linear(x, self.w_in)                                   # [T, 3 width (+ side rows)]: z | x | g | side
         out = torch.empty((x.shape[0], self.width), dtype=x.dtype, device=x.device)
         ops.mingru_scan(a, self.b_z, self.b_x, cache.state, ctx.q_start, ctx.state_slots, ctx.num_seqs, out, ctx.err,
                         max_q_len=ctx.max_q_len)
-        return linear(out, self.w_o)
+        y = linear(out, self.w_o)
+        return (y, a[:, 3 * self.width:]) if side else y
