@@ -298,42 +298,46 @@ latent_attention_mma_kernel(const bf16* q, bf16* out, const bf16* cache,
     }
 }
 
-// one warp per (sequence, row): the splits' partial results in order, and the sink
+// one CTA per (sequence, row): the splits' factors first (running max over the splits and the sink), then a
+// thread a value column adds the splits' partial sums in order
 __global__ void __launch_bounds__(128)
-latent_attention_merge_kernel(const float* work, bf16* out, const int* q_start,
-                              int heads, int dv, int dvp, int max_rows, int nsplit, const float* sink) {
+latent_attention_merge_kernel(const float* work, bf16* out, const int* q_start, int heads, int dv, int dvp,
+                              int max_rows, int nsplit, const float* sink) {
   pdl_wait();
   pdl_launch();
-  const int lane = threadIdx.x & 31;
-  const int row = blockIdx.x * 4 + (threadIdx.x >> 5), s = blockIdx.y;
+  extern __shared__ float fac[];      // [nsplit]: 2^(m_z - M), 0 for a split that saw nothing
+  __shared__ float red[32];
+  const int row = blockIdx.x, s = blockIdx.y;
   const int t0 = q_start[s], nq = q_start[s + 1] - t0;
   if (row >= nq * heads) return;
   const float* w = work + (((size_t)s * max_rows + row) * nsplit) * (dvp + 2);
   const float sk = sink ? sink[row % heads] * 1.4426950408889634f : -INFINITY;
-  float M = sk;
-  for (int z = 0; z < nsplit; ++z) M = fmaxf(M, w[(size_t)z * (dvp + 2) + dvp]);
-  float L = sink ? exp2f(sk - M) : 0.f;
-  float acc[16];
-#pragma unroll
-  for (int i = 0; i < 16; ++i) acc[i] = 0.f;
-  for (int z = 0; z < nsplit; ++z) {
-    const float* p = w + (size_t)z * (dvp + 2);
-    const float m = p[dvp], l = p[dvp + 1];
-    if (l <= 0.f || m == -INFINITY) continue;
-    const float f = exp2f(m - M);
-    L = fmaf(l, f, L);
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const int c = lane + 32 * i;
-      if (c < dv) acc[i] = fmaf(p[c], f, acc[i]);
-    }
+  float mx = sk;
+  for (int z = threadIdx.x; z < nsplit; z += blockDim.x) mx = fmaxf(mx, w[(size_t)z * (dvp + 2) + dvp]);
+  mx = warp_max(mx);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = mx;
+  __syncthreads();
+  const float M = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+  __syncthreads();
+  float part = 0.f;
+  for (int z = threadIdx.x; z < nsplit; z += blockDim.x) {
+    const float m = w[(size_t)z * (dvp + 2) + dvp], l = w[(size_t)z * (dvp + 2) + dvp + 1];
+    const float fz = (l > 0.f && m != -INFINITY) ? exp2f(m - M) : 0.f;
+    fac[z] = fz;
+    part += l * fz;
   }
+  part = block_sum(part, red);          // (its order depends on nsplit and the block size only)
+  const float L = part + (sink ? exp2f(sk - M) : 0.f);
   const float inv = L > 0.f ? 1.0f / L : 0.f;
   bf16* orow = out + ((size_t)t0 * heads + row) * dv;
-#pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    const int c = lane + 32 * i;
-    if (c < dv) orow[c] = __float2bfloat16_rn(acc[i] * inv);
+  for (int c = threadIdx.x; c < dv; c += blockDim.x) {
+    float acc = 0.f;
+    for (int z = 0; z < nsplit; ++z) {
+      const float fz = fac[z];
+      const float v = w[(size_t)z * (dvp + 2) + c];
+      acc = fmaf(fz != 0.f ? v : 0.f, fz, acc);
+    }
+    orow[c] = __float2bfloat16_rn(acc * inv);
   }
 }
 
@@ -359,8 +363,8 @@ static int lam_launch(const bf16* q, bf16* out, const bf16* cache, const int* bl
   RLLM_LAUNCH_CHECK();
   if (split_keys > 0) {
     const int max_rows = (int)blocks_x * ROWS;
-    dim3 mg((max_rows + 3) / 4, S);
-    rllm_launch_pdl(latent_attention_merge_kernel, dim3(mg), dim3(128), (size_t)(0), stream, work, out, q_start, heads, dv, 8 * NVT * NW, max_rows, nsplit, sink);
+    dim3 mg(max_rows, S);
+    rllm_launch_pdl(latent_attention_merge_kernel, dim3(mg), dim3(128), (size_t)nsplit * sizeof(float), stream, work, out, q_start, heads, dv, 8 * NVT * NW, max_rows, nsplit, sink);
     RLLM_LAUNCH_CHECK();
   }
   return 0;
@@ -384,7 +388,7 @@ RLLM_EXPORT int rllm_latent_attention_mma(const void* q, void* out, const void* 
                                           float scale, const float* sink, int split_keys, int nsplit, float* work,
                                           int* err, cudaStream_t stream) {
   if (S <= 0 || max_q <= 0) return 0;
-  if (split_keys > 0 && (split_keys % 64 != 0 || nsplit <= 0 || nsplit > 65535 || work == nullptr)) return RLLM_E_BADARG;
+  if (split_keys > 0 && (split_keys % 64 != 0 || nsplit <= 0 || nsplit > 8192 || work == nullptr)) return RLLM_E_BADARG;
   if (heads <= 0 || dk <= 0 || dv <= 0 || dv > dk || page_size <= 0 || num_pages <= 0 || max_blocks <= 0 ||
       window < 0)
     return RLLM_E_BADARG;

@@ -820,7 +820,7 @@ def latent_attention_mma(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor
     split_tiles, nsplit, work = 0, 1, None
     row_tiles = num_seqs * -(-(max_q_len * heads) // 64)
     keys = min(max_seq_len, window + max_q_len) if window else max_seq_len
-    if row_tiles <= LATENT_SPLIT_MAX_TILES and keys >= LATENT_SPLIT_MIN_KEYS:
+    if row_tiles <= LATENT_SPLIT_MAX_TILES and keys >= LATENT_SPLIT_MIN_KEYS and max_seq_len <= 8192 * LATENT_SPLIT_KEYS:
         split_tiles = LATENT_SPLIT_KEYS                     # in keys: a multiple of every key tile
         nsplit = -(-max_seq_len // LATENT_SPLIT_KEYS)
         lib.rllm_latent_attention_mma_work.restype = c_longlong
