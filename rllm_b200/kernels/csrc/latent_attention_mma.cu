@@ -102,24 +102,24 @@ latent_attention_mma_kernel(const bf16* q, bf16* out, const bf16* cache,
     l_cur[tid] = with_sink ? 1.f : 0.f;
   }
 
+  // four threads a key row: the row's page is looked up once a tile, its 16-byte chunks are shared out by fours
   auto load_keys = [&](int tile, int st) {
-    const int j0 = tile * LAM_KEYS;
-    bf16* dst = Ks + (size_t)st * LAM_KEYS * ld;
-    for (int c = tid; c < LAM_KEYS * chunks; c += LAM_THREADS) {
-      const int r = c / chunks, kc = (c - r * chunks) * 8;
-      const int j = j0 + r;
-      bool ok = j >= k_lo && j <= p_hi && kc < dk;
-      const bf16* src = cache;
-      if (ok) {
-        const int page = bt[j / page_size];
-        if (page < 0 || page >= num_pages) {
-          if (kc == 0) atomicOr(err, 4);
-          ok = false;
-        } else {
-          src = cache + ((size_t)page * page_size + (j % page_size)) * dk + kc;
-        }
+    const int r = tid >> 2, j = tile * LAM_KEYS + r;
+    bf16* dst = Ks + ((size_t)st * LAM_KEYS + r) * ld;
+    bool ok = j >= k_lo && j <= p_hi;
+    const bf16* src = cache;
+    if (ok) {
+      const int page = bt[j / page_size];
+      if (page < 0 || page >= num_pages) {
+        if ((tid & 3) == 0) atomicOr(err, 4);
+        ok = false;
+      } else {
+        src = cache + ((size_t)page * page_size + (j % page_size)) * dk;
       }
-      lam_cp16(dst + (size_t)r * ld + kc, src, ok);
+    }
+    for (int kc = (tid & 3) * 8; kc < chunks * 8; kc += 32) {
+      const bool here = ok && kc < dk;
+      lam_cp16(dst + kc, here ? (const void*)(src + kc) : (const void*)cache, here);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
