@@ -58,24 +58,57 @@ __device__ __forceinline__ void tgm_ldmatrix4(uint32_t (&r)[4], const void* smem
 // NT: n-tiles of 8 columns a warp owns (BM 64: 8, all 64 columns of its 16 rows; BM 16: 2)
 template <int BM> struct TgmShape { static constexpr int NT = (BM == 64) ? 8 : 2; };
 
+// What a thread copies in every stage, worked out once: its 16-byte chunk sits at the same k offset
+// (kc) of every row it serves, rows (tid + 128 i) / 4 of A and of each B matrix; a null pointer is zeros.
 template <int BM, int NB>
-__device__ __forceinline__ void tgm_load_stage(MmaTileSmem<BM, NB>& sm, int st, const bf16* const (&B)[NB],
-                                               long long ldb, int n0, int N, int K, int k0) {
+struct TgmPlan {
+  static constexpr int AS = (BM * 4 + TGM_THREADS - 1) / TGM_THREADS;
+  const bf16* a[AS];
+  const bf16* b[NB][2];
+  int kc;
+};
+
+template <int BM, int NB>
+__device__ __forceinline__ void tgm_plan(TgmPlan<BM, NB>& p, const MmaTileSmem<BM, NB>& sm, const bf16* const (&B)[NB],
+                                         long long ldb, int n0, int N) {
   const int tid = threadIdx.x;
-  for (int c = tid; c < BM * 4; c += TGM_THREADS) {
-    const int r = c >> 2, kc = (c & 3) * 8;
-    const bf16* p = (const bf16*)sm.rows[r];
-    const bool ok = p != nullptr && k0 + kc < K && k0 < K;
-    tgm_cp16(&sm.A[st][r][kc], ok ? (const void*)(p + k0 + kc) : (const void*)B[0], ok);
+  p.kc = (tid & 3) * 8;
+#pragma unroll
+  for (int i = 0; i < TgmPlan<BM, NB>::AS; ++i) {
+    const int r = (tid + TGM_THREADS * i) >> 2;
+    const bf16* row = (r < BM) ? (const bf16*)sm.rows[r] : nullptr;
+    p.a[i] = row ? row + p.kc : nullptr;
   }
 #pragma unroll
-  for (int b = 0; b < NB; ++b) {
-    for (int c = tid; c < TGM_BN * 4; c += TGM_THREADS) {
-      const int n = c >> 2, kc = (c & 3) * 8;
-      const bool ok = n0 + n < N && k0 + kc < K;
-      tgm_cp16(&sm.B[st][b * TGM_BN + n][kc], ok ? (const void*)(B[b] + (long long)(n0 + n) * ldb + k0 + kc) : (const void*)B[0], ok);
+  for (int b = 0; b < NB; ++b)
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int n = (tid + TGM_THREADS * i) >> 2;
+      p.b[b][i] = (n0 + n < N) ? B[b] + (long long)(n0 + n) * ldb + p.kc : nullptr;
+    }
+}
+
+template <int BM, int NB>
+__device__ __forceinline__ void tgm_load_stage(MmaTileSmem<BM, NB>& sm, int st, const TgmPlan<BM, NB>& p,
+                                               const void* dummy, int K, int k0) {
+  const int tid = threadIdx.x;
+  const bool in_k = k0 + p.kc < K;
+#pragma unroll
+  for (int i = 0; i < TgmPlan<BM, NB>::AS; ++i) {
+    const int r = (tid + TGM_THREADS * i) >> 2;
+    if (r < BM) {
+      const bool ok = in_k && p.a[i] != nullptr;
+      tgm_cp16(&sm.A[st][r][p.kc], ok ? (const void*)(p.a[i] + k0) : dummy, ok);
     }
   }
+#pragma unroll
+  for (int b = 0; b < NB; ++b)
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int n = (tid + TGM_THREADS * i) >> 2;
+      const bool ok = in_k && p.b[b][i] != nullptr;
+      tgm_cp16(&sm.B[st][b * TGM_BN + n][p.kc], ok ? (const void*)(p.b[b][i] + k0) : dummy, ok);
+    }
 }
 
 // acc[b][nt][4]: fragment of B matrix b, n-tile nt.  Element i of a fragment is output
@@ -98,8 +131,10 @@ __device__ __forceinline__ void tile_gemm_mma(MmaTileSmem<BM, NB>& sm, const bf1
   // a group is committed for every step of the ring, also an empty one, so that "all but the last
   // TGM_STAGES - 2 groups have landed" always means: the stage about to be read has
 #pragma unroll
+  TgmPlan<BM, NB> plan;
+  tgm_plan<BM, NB>(plan, sm, B, ldb, n0, N);
   for (int s = 0; s < TGM_STAGES - 1; ++s) {
-    if (s < steps) tgm_load_stage<BM, NB>(sm, s, B, ldb, n0, N, K, s * TGM_BK);
+    if (s < steps) tgm_load_stage<BM, NB>(sm, s, plan, B[0], K, s * TGM_BK);
     tgm_commit();
   }
   for (int s = 0; s < steps; ++s) {
@@ -107,7 +142,7 @@ __device__ __forceinline__ void tile_gemm_mma(MmaTileSmem<BM, NB>& sm, const bf1
     tgm_wait_ring();
     __syncthreads();               // stage st has landed for everyone, and everyone has left step s - 1
     if (s + TGM_STAGES - 1 < steps)
-      tgm_load_stage<BM, NB>(sm, (s + TGM_STAGES - 1) % TGM_STAGES, B, ldb, n0, N, K, (s + TGM_STAGES - 1) * TGM_BK);
+      tgm_load_stage<BM, NB>(sm, (s + TGM_STAGES - 1) % TGM_STAGES, plan, B[0], K, (s + TGM_STAGES - 1) * TGM_BK);
     tgm_commit();
 #pragma unroll
     for (int kk = 0; kk < TGM_BK; kk += 16) {
