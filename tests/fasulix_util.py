@@ -4,7 +4,10 @@ FX_A: every mixer kind; a window shorter than a page and one longer than two pag
 reads an earlier windowed layer's rows with ANOTHER window; a layer that reads a causal (sink)
 layer's rows; rot.dims smaller than rot_dim; dim != vdim; q_rank != kv_rank; one head; top 1, top
 == experts, an odd number of experts; a layer without a feed-forward; width and vocab no powers of two.
-FX_B: two layers, sizes that are multiples of 16 and 64 (other tile paths), a window of one.
+FX_B: three layers, sizes that are multiples of 16 and 64 (other tile paths), a window of one, no rotation in one layer.
+FX_C: recurrences first, then one attention layer whose sizes are multiples of 2 only (width 52, rows of 26
+values: none of the 16-byte paths applies), so a model may also keep no pages at all in its first layers.
+FX_D: recurrences only (no paged cache at all).
 """
 from __future__ import annotations
 
@@ -48,6 +51,23 @@ FX_B = {
          "mlp": _moe(8, 2, 64, 2.0)},
         {"type": "latent_attention", "mixer": _latent(2, 64, 0, 64, 128, 128, 100000.0), "mlp": _moe(2, 1, 128, 8.0)},
         {"type": "mingru", "mixer": {"width": 128}, "mlp": None},
+    ],
+}
+
+
+FX_C = {
+    "architecture": "Fasulix", "vocab": 97, "width": 52, "norm": {"eps": 1e-4},
+    "layers": [
+        {"type": "mingru", "mixer": {"width": 30}, "mlp": _moe(2, 2, 12, 1.0)},
+        {"type": "mingru", "mixer": {"width": 66}, "mlp": None},
+        {"type": "latent_attention", "mixer": _latent(5, 12, 6, 10, 22, 20, 3000.0, rot_dims=2), "mlp": _moe(7, 3, 10, 2.0)},
+    ],
+}
+FX_D = {
+    "architecture": "Fasulix", "vocab": 64, "width": 32, "norm": {"eps": 1e-6},
+    "layers": [
+        {"type": "mingru", "mixer": {"width": 48}, "mlp": _moe(4, 2, 16, 2.0)},
+        {"type": "mingru", "mixer": {"width": 16}, "mlp": _moe(4, 1, 16, 2.0)},
     ],
 }
 

@@ -3,7 +3,7 @@ import copy
 
 import pytest
 
-from fasulix_util import FX_A, FX_B
+from fasulix_util import FX_A, FX_B, FX_C, FX_D
 
 
 def _describe(cfg):
@@ -67,3 +67,12 @@ def test_llama_and_fasulix_are_both_registered():
     from rllm_b200.config import ARCHITECTURES, resolve_architecture
     resolve_architecture(FX_B)
     assert {"Fasulix", "LlamaForCausalLM"} <= set(ARCHITECTURES)
+
+
+def test_a_model_of_recurrences_only_keeps_no_pages():
+    from rllm_b200.parts.spec import StateNeed
+    spec, model = _describe(FX_D)
+    assert model.layout.groups == [StateNeed((48,)), StateNeed((16,))]
+    spec, model = _describe(FX_C)
+    assert [type(g).__name__ for g in model.layout.groups] == ["StateNeed", "StateNeed", "KVPagesNeed"]
+    assert model.layout.groups[2].head_dim == 26 and model.layout.groups[2].values is False

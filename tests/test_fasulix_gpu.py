@@ -9,7 +9,7 @@ import torch
 
 import plain_fasulix as pf
 import replay_util as ru
-from fasulix_util import FX_A, FX_B, sharpen, write_model
+from fasulix_util import FX_A, FX_B, FX_C, FX_D, sharpen, write_model
 
 pytestmark = pytest.mark.gpu
 
@@ -304,7 +304,9 @@ def test_gate_norm_add_and_the_depth_weighted_stream(dtype):
 @pytest.fixture(scope="module")
 def fx_dirs(tmp_path_factory):
     return {"A": write_model(str(tmp_path_factory.mktemp("fx_a")), FX_A, 11, sharpen),
-            "B": write_model(str(tmp_path_factory.mktemp("fx_b")), FX_B, 12, sharpen)}
+            "B": write_model(str(tmp_path_factory.mktemp("fx_b")), FX_B, 12, sharpen),
+            "C": write_model(str(tmp_path_factory.mktemp("fx_c")), FX_C, 13, sharpen),
+            "D": write_model(str(tmp_path_factory.mktemp("fx_d")), FX_D, 14, sharpen)}
 
 
 def plain_rows(folder, dtype, reqs):
@@ -346,14 +348,14 @@ def test_the_cuda_core_forms_of_the_bfloat16_kernels_still_serve(fx_dirs, monkey
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name,page", [("A", 16), ("A", 4), ("B", 8)])
+@pytest.mark.parametrize("name,page", [("A", 16), ("A", 4), ("B", 8), ("C", 16), ("D", 16)])
 def test_every_way_of_cutting_gives_the_plain_logits(fx_dirs, name, page, dtype):
     """Whole prompts, token by token from the first token on, portions down to two tokens, and mixed
     batches of up to four live requests whose pages and slots are given back and used again (the pool
     holds exactly the peak); every position's logits are compared."""
-    cfg = FX_A if name == "A" else FX_B
+    cfg = {"A": FX_A, "B": FX_B, "C": FX_C, "D": FX_D}[name]
     V = cfg["vocab"]
-    reqs = make_requests(V, [61, 1, 2, 17, 90, 33, 5], seed=7)
+    reqs = make_requests(V, [61, 1, 2, 17, 90, 33, 5] + ([150] if name in "CD" else []), seed=7)
     want = plain_rows(fx_dirs[name], dtype, reqs)
     for what, tb in (("whole", ru.trace_whole(reqs)), ("one by one", ru.trace_tail_decode(reqs, tail=1000)),
                      ("tail decoded", ru.trace_tail_decode(reqs, tail=45)),
