@@ -13,8 +13,9 @@ experts, or none.  Keys:
                       mask: {size} (latent_attention_2), kv_from (optional)}
       mlp:           {kind: "moe", expert: {ff, limit}, router: {experts, top}}
 
-Every size and constant is taken from these keys; optional ``max_positions`` bounds
-a request's length for the engine (the design itself has no bound).
+Every size and constant is taken from these keys; optional ``max_positions`` (default
+131,072) bounds a request's length for the engine, which sizes its cache pools by it (the
+design itself has no bound, and trace replay does not look at it).
 """
 from __future__ import annotations
 
@@ -63,7 +64,7 @@ class FasulixConfig:
     width: int
     eps: float
     layers: Tuple[FasulixLayer, ...]
-    max_positions: int = 1 << 20
+    max_positions: int = 1 << 17
     torch_dtype: str = "bfloat16"
 
     @staticmethod
@@ -133,5 +134,5 @@ class FasulixConfig:
         return FasulixConfig(vocab=int(need(raw, "vocab", "the configuration")),
                              width=int(need(raw, "width", "the configuration")),
                              eps=float(need(need(raw, "norm", "the configuration"), "eps", "norm")),
-                             layers=tuple(layers), max_positions=int(raw.get("max_positions", 1 << 20)),
+                             layers=tuple(layers), max_positions=int(raw.get("max_positions", 1 << 17)),
                              torch_dtype=str(raw.get("torch_dtype", "bfloat16")))
