@@ -21,7 +21,7 @@
 #include "common.cuh"
 #include <math.h>
 
-// NW warps a CTA (4, or 8 where the values are wider than 256: their columns are shared out among more
+// NW warps a CTA (4, or 8 where the values are wider than 64: their columns are shared out among more
 // warps); a key tile has 8 keys a warp.
 
 __device__ __forceinline__ void lam_cp16(void* smem_dst, const void* src, bool valid) {
@@ -59,8 +59,10 @@ latent_attention_mma_kernel(const bf16* q, bf16* out, const bf16* cache,
 
   const int s = blockIdx.y;
   const int t0 = q_start[s], nq = q_start[s + 1] - t0;
-  const int row_base = blockIdx.x * ROWS;                   // among the sequence's nq * heads rows
-  if (row_base >= nq * heads) return;
+  // among the sequence's nq * heads rows; the last rows see the most keys, so they are handed out first
+  const int row_tiles = (nq * heads + ROWS - 1) / ROWS;
+  if ((int)blockIdx.x >= row_tiles) return;
+  const int row_base = (row_tiles - 1 - (int)blockIdx.x) * ROWS;
   const int seq_len = seq_lens[s];
   const int pos0 = seq_len - nq;                            // position of the sequence's first token of this step
   const int rows_here = min(ROWS, nq * heads - row_base);
@@ -150,11 +152,11 @@ latent_attention_mma_kernel(const bf16* q, bf16* out, const bf16* cache,
     if (tile < tile_hi) load_keys(tile + 1, st ^ 1);
     const bf16* K = Ks + (size_t)st * LAM_KEYS * ld;
     // ---- scores of keys 8 warp .. 8 warp + 7 for all rows
-    float sc[MT][4];
+    float sc[MT][4], sc2[MT][4];       // even and odd k steps add up apart: twice as many MMAs in flight
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-      for (int i = 0; i < 4; ++i) sc[mt][i] = 0.f;
+      for (int i = 0; i < 4; ++i) sc[mt][i] = sc2[mt][i] = 0.f;
     // two k steps of 16 a round: one ldmatrix.x4 brings the keys' fragments of both (8 keys x 32 values),
     // one ldmatrix.x4 per row tile and k step the queries'
     const unsigned kaddr = (unsigned)__cvta_generic_to_shared(K + (size_t)(warp * 8 + (lane & 7)) * ld + (lane >> 3) * 8);
@@ -171,10 +173,15 @@ latent_attention_mma_kernel(const bf16* q, bf16* out, const bf16* cache,
           asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                        : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3])
                        : "r"(qaddr + (unsigned)((mt * 16 * ld + (ks + half) * 16) * 2)));
-          lam_mma(sc[mt], a, b[2 * half], b[2 * half + 1]);
+          if (half == 0) lam_mma(sc[mt], a, b[0], b[1]);
+          else lam_mma(sc2[mt], a, b[2], b[3]);
         }
       }
     }
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) sc[mt][i] += sc2[mt][i];
     const int jbase = tile * LAM_KEYS + warp * 8 + 2 * t;
     float* wm = wmax + (size_t)par * NW * ROWS;
     float* ws = wsum + (size_t)par * NW * ROWS;
@@ -253,15 +260,33 @@ latent_attention_mma_kernel(const bf16* q, bf16* out, const bf16* cache,
         asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                      : "=r"(a[mt][0]), "=r"(a[mt][1]), "=r"(a[mt][2]), "=r"(a[mt][3]) : "r"(paddr));
       }
+      if constexpr (NVT % 2 == 0) {
 #pragma unroll
-      for (int nt = 0; nt < NVT; ++nt) {
-        // V^T fragment: keys kk .. kk+15 (rows of K), columns col .. col+7; lanes 0-15 give the row addresses
-        const int col = (warp * NVT + nt) * 8;
-        const unsigned addr = (unsigned)__cvta_generic_to_shared(K + (size_t)(kk + (lane & 15)) * ld + col);
-        uint32_t b0, b1;
-        asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(b0), "=r"(b1) : "r"(addr));
+        for (int nt = 0; nt < NVT; nt += 2) {
+          // V^T fragments of two n-tiles: keys kk .. kk+15 (rows of K), columns col .. col+15
+          const int col = (warp * NVT + nt) * 8;
+          const unsigned addr = (unsigned)__cvta_generic_to_shared(
+              K + (size_t)(kk + (lane & 7) + ((lane >> 3) & 1) * 8) * ld + col + ((lane >> 4) & 1) * 8);
+          uint32_t b[4];
+          asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                       : "=r"(b[0]), "=r"(b[1]), "=r"(b[2]), "=r"(b[3]) : "r"(addr));
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt) lam_mma(o[mt][nt], a[mt], b0, b1);
+          for (int mt = 0; mt < MT; ++mt) {
+            lam_mma(o[mt][nt], a[mt], b[0], b[1]);
+            lam_mma(o[mt][nt + 1], a[mt], b[2], b[3]);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int nt = 0; nt < NVT; ++nt) {
+          // V^T fragment: keys kk .. kk+15 (rows of K), columns col .. col+7; lanes 0-15 give the row addresses
+          const int col = (warp * NVT + nt) * 8;
+          const unsigned addr = (unsigned)__cvta_generic_to_shared(K + (size_t)(kk + (lane & 15)) * ld + col);
+          uint32_t b0, b1;
+          asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(b0), "=r"(b1) : "r"(addr));
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) lam_mma(o[mt][nt], a[mt], b0, b1);
+        }
       }
     }
   }
@@ -409,8 +434,8 @@ RLLM_EXPORT int rllm_latent_attention_mma(const void* q, void* out, const void* 
   } while (0)
   if (dv <= 32) LAM_PICK(1, 4, 4);
   if (dv <= 64) LAM_PICK(2, 4, 4);
-  if (dv <= 128) LAM_PICK(4, 4, 4);
-  if (dv <= 256) LAM_PICK(8, 4, 4);
+  if (dv <= 128) LAM_PICK(2, 4, 8);
+  if (dv <= 256) LAM_PICK(4, 4, 8);
   LAM_PICK(8, 2, 8);
 #undef LAM_PICK
 #undef LAM_GO
