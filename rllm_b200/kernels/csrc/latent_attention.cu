@@ -198,14 +198,13 @@ head_gemm_mma_kernel(const bf16* A, long long lda, long long a_head, const bf16*
   float acc[1][TgmShape<BM>::NT][4];
   const bf16* const Bh[1] = {B + (size_t)h * b_head};
   tile_gemm_mma<BM, 1>(sm, Bh, ldb, n0, N, K, acc);
-  int row0, col0;
-  tgm_origin<BM>(row0, col0);
-  const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
 #pragma unroll
   for (int nt = 0; nt < TgmShape<BM>::NT; ++nt)
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const int m = m0 + row0 + g + 8 * (i >> 1), n = n0 + col0 + nt * 8 + 2 * t + (i & 1);
+      int tr, tc;
+      tgm_coord<BM>(nt, i, tr, tc);
+      const int m = m0 + tr, n = n0 + tc;
       if (m < M && n < N) C[(size_t)m * ldc + (size_t)h * c_head + n] = __float2bfloat16_rn(acc[0][nt][i]);
     }
 }

@@ -286,14 +286,13 @@ moe_gate_up_mma_kernel(const bf16* h, const bf16* w, bf16* y,
   const bf16* we = w + (size_t)e * 2 * F * H;
   const bf16* const B[2] = {we, we + (size_t)F * H};
   tile_gemm_mma<BM, 2>(sm, B, H, n0, F, H, acc);
-  int row0, col0;
-  tgm_origin<BM>(row0, col0);
-  const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
 #pragma unroll
   for (int nt = 0; nt < TgmShape<BM>::NT; ++nt)
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const int r = r0 + row0 + g + 8 * (i >> 1), n = n0 + col0 + nt * 8 + 2 * t + (i & 1);
+      int tr, tc;
+      tgm_coord<BM>(nt, i, tr, tc);
+      const int r = r0 + tr, n = n0 + tc;
       if (r >= rend || n >= F) continue;
       const float gg = fminf(acc[0][nt][i], limit), uu = fminf(fmaxf(acc[1][nt][i], -limit), limit);
       y[(size_t)r * F + n] = __float2bfloat16_rn(gg * (1.0f / (1.0f + expf(-alpha * gg))) * (uu + 1.0f));
@@ -321,14 +320,13 @@ moe_down_mma_kernel(const bf16* y, const bf16* w, bf16* out,
   float acc[1][TgmShape<BM>::NT][4];
   const bf16* const B[1] = {w + (size_t)e * H * F};
   tile_gemm_mma<BM, 1>(sm, B, F, n0, H, F, acc);
-  int row0, col0;
-  tgm_origin<BM>(row0, col0);
-  const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
 #pragma unroll
   for (int nt = 0; nt < TgmShape<BM>::NT; ++nt)
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const int r = r0 + row0 + g + 8 * (i >> 1), n = n0 + col0 + nt * 8 + 2 * t + (i & 1);
+      int tr, tc;
+      tgm_coord<BM>(nt, i, tr, tc);
+      const int r = r0 + tr, n = n0 + tc;
       if (r >= rend || n >= H) continue;
       out[(size_t)sorted[r] * H + n] = __float2bfloat16_rn(acc[0][nt][i]);
     }

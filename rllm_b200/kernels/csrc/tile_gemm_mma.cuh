@@ -111,16 +111,30 @@ __device__ __forceinline__ void tgm_load_stage(MmaTileSmem<BM, NB>& sm, int st, 
     }
 }
 
-// acc[b][nt][4]: fragment of B matrix b, n-tile nt.  Element i of a fragment is output
-// (row, col) = (row0 + lane / 4 + 8 * (i / 2), col0 + nt * 8 + 2 * (lane % 4) + (i & 1)),
-// with (row0, col0) from tgm_origin.
+// How the tile is shared out.  BM 64: the four warps form a 2 x 2 grid of 32 x 32 outputs (two row tiles of
+// 16 by four n-tiles of 8 a warp), so a warp reads half of A's and half of B's rows of a stage.  BM 16: a warp
+// owns 16 columns (two n-tiles) of the 16 rows.  acc[b][nt][4] holds B matrix b's fragments, nt = row tile * NTL
+// + n-tile; tgm_coord gives the output (row, col) within the CTA's tile of element i of fragment nt.
+template <int BM>
+__device__ __forceinline__ void tgm_coord(int nt, int i, int& row, int& col) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+  if (BM == 64) {
+    row = (warp >> 1) * 32 + (nt >> 2) * 16 + g + 8 * (i >> 1);
+    col = (warp & 1) * 32 + (nt & 3) * 8 + 2 * t + (i & 1);
+  } else {
+    row = g + 8 * (i >> 1);
+    col = warp * 16 + nt * 8 + 2 * t + (i & 1);
+  }
+}
+
 template <int BM, int NB>
 __device__ __forceinline__ void tile_gemm_mma(MmaTileSmem<BM, NB>& sm, const bf16* const (&B)[NB], long long ldb,
                                               int n0, int N, int K, float (&acc)[NB][TgmShape<BM>::NT][4]) {
   constexpr int NT = TgmShape<BM>::NT;
+  constexpr int MTW = (BM == 64) ? 2 : 1, NTL = NT / MTW;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int row0 = (BM == 64) ? warp * 16 : 0;
-  const int col0 = (BM == 64) ? 0 : warp * 16;
+  const int row0 = (BM == 64) ? (warp >> 1) * 32 : 0;
+  const int col0 = (BM == 64) ? (warp & 1) * 32 : warp * 16;
 #pragma unroll
   for (int b = 0; b < NB; ++b)
 #pragma unroll
@@ -130,7 +144,6 @@ __device__ __forceinline__ void tile_gemm_mma(MmaTileSmem<BM, NB>& sm, const bf1
   const int steps = (K + TGM_BK - 1) / TGM_BK;
   // a group is committed for every step of the ring, also an empty one, so that "all but the last
   // TGM_STAGES - 2 groups have landed" always means: the stage about to be read has
-#pragma unroll
   TgmPlan<BM, NB> plan;
   tgm_plan<BM, NB>(plan, sm, B, ldb, n0, N);
   for (int s = 0; s < TGM_STAGES - 1; ++s) {
@@ -147,27 +160,25 @@ __device__ __forceinline__ void tile_gemm_mma(MmaTileSmem<BM, NB>& sm, const bf1
 #pragma unroll
     for (int kk = 0; kk < TGM_BK; kk += 16) {
       // fragments by ldmatrix: A's 16 x 16 in one, B's 8 x 16 of two n-tiles in one
-      uint32_t a[4];
-      tgm_ldmatrix4(a, &sm.A[st][row0 + (lane & 15)][kk + (lane >> 4) * 8]);
+      uint32_t a[MTW][4];
+#pragma unroll
+      for (int mt = 0; mt < MTW; ++mt)
+        tgm_ldmatrix4(a[mt], &sm.A[st][row0 + mt * 16 + (lane & 15)][kk + (lane >> 4) * 8]);
 #pragma unroll
       for (int b = 0; b < NB; ++b)
 #pragma unroll
-        for (int nt = 0; nt < NT; nt += 2) {
+        for (int nt = 0; nt < NTL; nt += 2) {
           uint32_t bb[4];
           tgm_ldmatrix4(bb, &sm.B[st][b * TGM_BN + col0 + nt * 8 + (lane & 7) + ((lane >> 4) & 1) * 8][kk + ((lane >> 3) & 1) * 8]);
-          tgm_mma(acc[b][nt], a, bb[0], bb[1]);
-          tgm_mma(acc[b][nt + 1], a, bb[2], bb[3]);
+#pragma unroll
+          for (int mt = 0; mt < MTW; ++mt) {
+            tgm_mma(acc[b][mt * NTL + nt], a[mt], bb[0], bb[1]);
+            tgm_mma(acc[b][mt * NTL + nt + 1], a[mt], bb[2], bb[3]);
+          }
         }
     }
   }
   __syncthreads();
-}
-
-template <int BM>
-__device__ __forceinline__ void tgm_origin(int& row0, int& col0) {
-  const int warp = threadIdx.x >> 5;
-  row0 = (BM == 64) ? warp * 16 : 0;
-  col0 = (BM == 64) ? 0 : warp * 16;
 }
 
 // whether RLLM_TILE_GEMM=simt keeps these products on the CUDA cores (for tests and comparisons)

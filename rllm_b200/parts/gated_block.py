@@ -76,6 +76,13 @@ class SandwichGatedBlock(Part):
             specs.append(TensorSpec(n["depth"], (self.depth_levels,), role="vector", init=("one_plus_normal", 0.3)))
         return specs
 
+    def ignored_tensors(self) -> List[str]:
+        """A layer without a feed-forward uses neither its second gate nor its last two norms: a file that
+        carries them all the same is no error."""
+        if self.ffn is not None:
+            return []
+        return [self.names["gate2"], self.names["gate2_bias"]] + [n.name for n in self.norms[2:] if hasattr(n, "name")]
+
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
         n = self.names
         self.w_g1, self.b_g1 = tensors[n["gate1"]], tensors[n["gate1_bias"]].contiguous()

@@ -86,6 +86,12 @@ class LatentAttention(Mixer):
         specs.append(TensorSpec(n["o"], (self.hidden, H * self.vdim)))
         return specs
 
+    def ignored_tensors(self) -> List[str]:
+        """What a file may carry for a layer that does not use it: the down projection of a layer that reads
+        another layer's rows, a sink where the softmax has none."""
+        n = self.names
+        return ([n["dkv"], n["dkv_norm"]] if self.shares_kv else []) + ([] if self.has_sink else [n["sink"]])
+
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
         n, H = self.names, self.heads
         if self.shares_kv:

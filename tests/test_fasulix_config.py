@@ -26,7 +26,9 @@ def test_the_architecture_is_found_by_its_name_and_every_size_comes_from_the_con
     assert "l2.mix.sink" not in shapes and "l3.mix.dkv" not in shapes and "l3.mix.dkv.norm" not in shapes
     assert shapes["l1.mix.z"] == (72, 88) and shapes["l1.mix.x.b"] == (72,) and shapes["l1.mix.o"] == (88, 72)
     assert shapes["l1.mlp.router"] == (3, 88) and shapes["l1.mlp.e2.down"] == (88, 40)
-    assert "l2.mlp.router" not in shapes and "l2.rg2" not in shapes and "l2.norm2" in shapes or True
+    assert "l2.mlp.router" not in shapes and "l2.rg2" not in shapes and "l2.norm2" not in shapes   # no feed-forward
+    ignored = [n for part in model.parts() for n in part.ignored_tensors()]
+    assert {"l2.rg2", "l2.rg2.b", "l2.norm2", "l2.norm2b", "l3.mix.dkv", "l3.mix.dkv.norm", "l2.mix.sink"} <= set(ignored)
     assert [shapes[f"l{i}.dwa"] for i in range(6)] == [(i + 2,) for i in range(6)]
     assert shapes["l4.rg1"] == (88, 88) and shapes["l4.rg2.b"] == (88,)
 
