@@ -510,3 +510,29 @@ def test_decoding_over_long_rows_cuts_the_keys_into_splits(window, sink, heads, 
             den = e.sum() + (math.exp(float(sk[h]) - top) if sink else 0.0)
             want[s, h] = (e / den) @ rd[lo:n, :dv]
     assert rel(out.view(2, heads, dv), want) <= 2e-2
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_forked_request_shares_full_pages_and_copies_the_last_page_and_the_state(fx_dirs, dtype):
+    """A parent feeds 21 tokens (pages of 8: two full pages and a partly filled one in every paged group, a
+    state slot per recurrence), a child is forked from it and both go on with different tokens, in portions and
+    token by token: the child's one-row pages and state slot start as copies, and neither disturbs the other."""
+    V = FX_A["vocab"]
+    rng = np.random.default_rng(31)
+    common, tail_p, tail_c = ([int(t) for t in rng.integers(0, V, size=n)] for n in (21, 30, 30))
+    tb = ru.TraceBuilder()
+    tb.step([("p", common)])
+    tb.step([("p", tail_p[:1]), ("c", tail_c[:7])], fork=[("p", "c")])
+    for i in range(1, 20):
+        tb.step([("p", tail_p[i:i + 1]), ("c", tail_c[6 + i:7 + i])])
+    tb.step([("p", tail_p[20:]), ("c", tail_c[26:])], end=["p", "c"])
+    got = ru.run_trace(fx_dirs["A"], dtype, tb, V, page_size=8)
+    reqs = {"p": common + tail_p, "c": common + tail_c}
+    want = plain_rows(fx_dirs["A"], dtype, reqs)
+    assert max(pos for r, pos in got if r == "c") == len(reqs["c"]) - 1
+    over = 0
+    for (r, pos), row in got.items():
+        err = np.abs(row - want[r][pos]).max() / np.abs(want[r]).max()
+        assert dtype == "bfloat16" or err <= TOL[dtype], (r, pos, float(err))
+        over += err > TOL[dtype]
+    assert over <= 0.03 * len(got)
