@@ -623,13 +623,26 @@ def logprobs(logits: torch.Tensor, tokens: torch.Tensor, top_n: int):
 def gated_postnorm_add(x_in: torch.Tensor, x_out: torch.Tensor, y: torch.Tensor, gate: torch.Tensor,
                        gate_bias: torch.Tensor, norm_weight: torch.Tensor, eps: float,
                        slot_weights: Optional[torch.Tensor] = None,
-                       next_weight: Optional[torch.Tensor] = None, next_eps: float = 0.0) -> Optional[torch.Tensor]:
+                       next_weight: Optional[torch.Tensor] = None, next_eps: float = 0.0,
+                       depth=None) -> Optional[torch.Tensor]:
     """x_out = x_in + rmsnorm(v) * norm_weight with v = y * sigmoid(gate + gate_bias); x float32 [T, H]
     (x_out may be x_in).  ``slot_weights`` float32 [T, K]: y is [T * K, H] and a token's K rows are added
     with these factors first.  ``gate`` [T, H] may be a column slice (row stride >= H).  With
-    ``next_weight`` the RMS norm of the new x under that weight is returned in the activation dtype."""
+    ``next_weight`` the RMS norm of the new x under that weight is returned in the activation dtype.
+    ``depth`` = (history float32 [L, T, H] whose level ``levels - 1`` is ``x_out``, levels, coeff [levels],
+    stream_out float32 [T, H]): the depth average sum_j coeff[j] history[j] is written to ``stream_out`` in the
+    same kernel, and the returned norm is the norm of that sum."""
     lib = build.load_library("layer_glue")
     T, H = x_in.shape
+    hist = coeff = stream_out = None
+    level_stride = levels = 0
+    if depth is not None:
+        hist, levels, coeff, stream_out = depth
+        assert hist.dtype is torch.float32 and hist.is_contiguous() and hist.shape[1:] == (T, H) and 1 <= levels <= hist.shape[0]
+        assert x_out.data_ptr() == hist[levels - 1].data_ptr() and coeff.numel() == levels and coeff.is_contiguous()
+        assert coeff.dtype is norm_weight.dtype and stream_out.dtype is torch.float32 and stream_out.shape == (T, H)
+        _contig(stream_out, "stream_out")
+        level_stride = hist.stride(0)
     assert x_in.dtype is torch.float32 and x_out.dtype is torch.float32 and x_out.shape == x_in.shape
     _contig(x_in, "x_in"); _contig(x_out, "x_out"); _contig(y, "y")
     slots = 1
@@ -646,7 +659,8 @@ def gated_postnorm_add(x_in: torch.Tensor, x_out: torch.Tensor, y: torch.Tensor,
     _check(lib.rllm_gated_postnorm_add(_ptr(x_in), _ptr(x_out), _ptr(y), c_int(slots), _ptr(slot_weights),
                                        _ptr(gate), c_int(gate.stride(0) if T > 1 else max(H, gate.stride(0))),
                                        _ptr(gate_bias), _ptr(norm_weight), c_float(eps), _ptr(next_weight),
-                                       _ptr(nxt), c_float(next_eps), c_int(T), c_int(H),
+                                       _ptr(nxt), c_float(next_eps), _ptr(hist), c_longlong(level_stride),
+                                       c_int(levels), _ptr(coeff), _ptr(stream_out), c_int(T), c_int(H),
                                        c_int(dtype_code(y.dtype)), c_int(dtype_code(norm_weight.dtype)),
                                        _stream()), "gated_postnorm_add")
     return nxt

@@ -12,8 +12,9 @@ the next layer (or the output) reads is  sum_{j < n} d[j] X_j  with the layer's
 learned d.  The results X_j are float32 and kept for the whole step
 (``ctx.extras["depth_history"]``, made by the model); gate, norms, adds and the
 weighted sum are float32 arithmetic.  The gate's sigmoid, the norm of the gated
-result, the add and the norm that reads the stream next are one kernel; so are the
-weighted sum over the depth and the next layer's first norm.  The mixer's gate product
+result, the add and the norm that reads the stream next are one kernel; the kernel of
+the layer's last sublayer also takes the weighted sum over the depth and the next layer's
+first norm (``ops.depth_average`` is that sum alone, for readers that want only some rows).  The mixer's gate product
 joins the mixer's own first product where the mixer stacks its input weights
 (``Mixer.stack_input``).
 
@@ -120,9 +121,12 @@ class SandwichGatedBlock(Part):
             m = self.mixer.forward(a, ctx, cache)
             g = linear(a, self.w_g1)
         last = self.ffn is None
-        direct = nxt_w if (last and not self.depth_levels) else None
+        # the sublayer that ends the layer also takes the depth average and the next layer's first norm
+        stream = torch.empty_like(h) if self.depth_levels else None
+        depth = (ctx.extras["depth_history"], self.depth_levels, self.depth, stream) if self.depth_levels else None
         b = ops.gated_postnorm_add(h, x, m, g, self.b_g1, n1.weight, n1.eps,
-                                   next_weight=direct if last else n2.weight, next_eps=nxt_eps if last else n2.eps)
+                                   next_weight=nxt_w if last else n2.weight, next_eps=nxt_eps if last else n2.eps,
+                                   depth=depth if last else None)
         normed = b if last else None
         if not last:
             if hasattr(self.ffn, "forward_slots"):
@@ -130,12 +134,8 @@ class SandwichGatedBlock(Part):
             else:
                 f, slot_w = self.ffn.forward(b), None
             g = linear(b, self.w_g2)
-            direct = nxt_w if not self.depth_levels else None
             normed = ops.gated_postnorm_add(x, x, f, g, self.b_g2, n3.weight, n3.eps, slot_weights=slot_w,
-                                            next_weight=direct, next_eps=nxt_eps)
+                                            next_weight=nxt_w, next_eps=nxt_eps, depth=depth)
         if self.depth_levels:
-            stream = torch.empty_like(h)
-            normed = ops.depth_average(ctx.extras["depth_history"], self.depth_levels, self.depth, stream, nxt_w,
-                                       nxt_eps, ctx.act_dtype)
             x = stream
         return x, (NormedRows(normed, nxt_w, nxt_eps) if normed is not None and nxt_w is not None else None)

@@ -296,6 +296,16 @@ def test_gate_norm_add_and_the_depth_weighted_stream(dtype):
     rows = torch.tensor([4, 1], dtype=torch.int32, device="cuda")
     n3 = ops.depth_average(hist, L, coeff.cuda(), None, nw.cuda(), 1e-5, DT[dtype], rows=rows)
     assert torch.equal(n3, n2[[4, 1]])
+    # both in one kernel: the layer's result goes to the history's last level, the stream is the weighted sum
+    hist2 = hist.clone()
+    stream2 = torch.empty(T, H, device="cuda")
+    n4 = ops.gated_postnorm_add(x.cuda(), hist2[L - 1], y.cuda(), gate.cuda()[:, :H], gb.cuda(), nw.cuda(), 1e-5,
+                                slot_weights=sw.cuda(), next_weight=nxt.cuda(), next_eps=1e-3,
+                                depth=(hist2, L, coeff.cuda(), stream2))
+    assert rel(hist2[L - 1], want) <= 2e-6
+    ws2 = (hist[:L - 1].double().cpu() * coeff.double()[:L - 1, None, None]).sum(0) + coeff.double()[L - 1] * want
+    assert rel(stream2, ws2) <= 2e-6
+    assert rel(n4, pf.unit_rms(ws2, nxt.double(), 1e-3)) <= (2e-6 if dtype == "float32" else 1e-2)
 
 
 # ---------------------------------------------------------------------------
