@@ -8,7 +8,8 @@ Inside a page the tokens of one kv head are contiguous rows of head_dim, so a
 (page, head) tile is one contiguous block (the reference's
 [blocks, heads, head_dim, block_size], spec.rs:63-68, strides the hot axis).
 State group: every owning run gets float32 [max_seqs, *shape], indexed by a
-request's state slot.  All storage is allocated once, here.
+request's state slot.  A mixer that declared several needs (pages and state,
+or two states) owns storage in several groups.  All storage is allocated once, here.
 
 Every paged buffer has one page more than the manager hands out: page
 ``spare_page(group)`` belongs to no request; every state buffer has one slot
@@ -27,7 +28,8 @@ from ..parts.spec import KVPagesNeed, StateNeed
 
 def page_bytes(need: KVPagesNeed, page_size: int, elem_size: int) -> int:
     """Bytes of one page of one run: K and V (one buffer where keys serve as values)."""
-    return (2 if need.values else 1) * need.num_kv_heads * page_size * need.head_dim * elem_size
+    row = need.head_dim + (need.value_dim if need.values else 0)
+    return need.num_kv_heads * page_size * row * elem_size
 
 
 class CacheStorage:
@@ -45,8 +47,9 @@ class CacheStorage:
             for run in layout.owners[g]:
                 if isinstance(need, KVPagesNeed):
                     shape = (pages_of[g] + 1, need.num_kv_heads, page_size, need.head_dim)
+                    vshape = shape[:3] + (need.value_dim,)
                     self.kv[run] = (torch.zeros(shape, dtype=dtype, device=device),
-                                    torch.zeros(shape, dtype=dtype, device=device) if need.values else None)
+                                    torch.zeros(vshape, dtype=dtype, device=device) if need.values else None)
                 elif isinstance(need, StateNeed):
                     self.state[run] = torch.zeros((max_seqs + 1,) + tuple(need.shape), dtype=torch.float32,
                                                   device=device)
@@ -58,15 +61,22 @@ class CacheStorage:
         return self._pages_of[group]
 
     def view(self, run_index: int):
+        """The cache view of a run's mixer; a tuple of views, in the order of its needs, for a mixer that
+        declared several (their storage is keyed (owning run, number of the need))."""
         g = self.layout.run_group[run_index]
         if g is None:
             return None
         owner = self.layout.run_owner[run_index]
         writes = owner == run_index
-        if owner in self.kv:
-            k, v = self.kv[owner]
+        if isinstance(g, tuple):
+            return tuple(self._view((owner, j), gj, writes) for j, gj in enumerate(g))
+        return self._view(owner, g, writes)
+
+    def _view(self, key, g: int, writes: bool):
+        if key in self.kv:
+            k, v = self.kv[key]
             return KVCacheView(k, v, g, writes)
-        return StateCacheView(self.state[owner], g, writes)
+        return StateCacheView(self.state[key], g, writes)
 
     def zero_slots(self, slots: List[int]) -> None:
         """Zero the state of newly handed-out slots."""

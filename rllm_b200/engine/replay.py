@@ -20,7 +20,7 @@ multiple of 64); the page pool is made for exactly that many, so pages of
 finished requests are used again.  An optional key ``"fork": [{"from": "a", "to": "b"}]`` makes request ``b``, before the
 step's entries run, a copy of everything ``a`` has been fed so far (shared full
 pages, a copied last page and state slot); both go on independently.
-``--max-live`` (8) is the most requests
+``--max-live`` (4) is the most requests
 that are live at a time; a trace that exceeds either limit ends with exit code
 3 and a message that names the step.
 
@@ -46,7 +46,7 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--max-tokens", type=int, required=True,
                    help="most tokens live requests hold at any time")
     p.add_argument("--block-size", type=int, default=PAGE_SIZE, help="tokens per cache page")
-    p.add_argument("--max-live", type=int, default=8,
+    p.add_argument("--max-live", type=int, default=4,
                    help="most requests that are live at a time (state slots of the cache manager)")
     p.add_argument("--device", default="cuda:0")
     return p

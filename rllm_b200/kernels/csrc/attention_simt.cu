@@ -37,13 +37,15 @@ template <> struct Vec8<bf16> {
   }
 };
 
-template <typename T>
+// d: the size of a query and key head; dv: of a value and output head (they may differ).  VEC: d is a
+// multiple of 8 and keys are fetched eight at a time; otherwise one by one.
+template <typename T, bool VEC>
 __global__ void __launch_bounds__(32 * ATT_WARPS)
 attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out,
                       const T* __restrict__ kcache, const T* __restrict__ vcache,
                       const int* __restrict__ block_table, int max_blocks,
                       const int* __restrict__ positions, const int* __restrict__ token_seq, int T_tokens,
-                      int nq, int nkv, int d, int page_size, int num_pages, int window, float scale,
+                      int nq, int nkv, int d, int dv, int page_size, int num_pages, int window, float scale,
                       int* __restrict__ err) {
   extern __shared__ float qs[];  // [ATT_WARPS][d]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -79,11 +81,15 @@ attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
       } else {
         const T* kp = kcache + (((size_t)page * nkv + kvh) * page_size + (j % page_size)) * d;
         float dot = 0.f;
-        for (int i = 0; i < d; i += 8) {
-          float kv[8];
-          Vec8<T>::load(kp + i, kv);
+        if (VEC) {
+          for (int i = 0; i < d; i += 8) {
+            float kv[8];
+            Vec8<T>::load(kp + i, kv);
 #pragma unroll
-          for (int u = 0; u < 8; ++u) dot = fmaf(myq[i + u], kv[u], dot);
+            for (int u = 0; u < 8; ++u) dot = fmaf(myq[i + u], kv[u], dot);
+          }
+        } else {
+          for (int i = 0; i < d; ++i) dot = fmaf(myq[i], to_f32(kp[i]), dot);
         }
         score = dot * scale;
       }
@@ -102,21 +108,47 @@ attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
       const float pj = __shfl_sync(0xffffffffu, p, jj);
       const int pg = __shfl_sync(0xffffffffu, page, jj);
       if (pg < 0) continue;
-      const T* vp = vcache + (((size_t)pg * nkv + kvh) * page_size + ((j0 + jj) % page_size)) * d;
+      const T* vp = vcache + (((size_t)pg * nkv + kvh) * page_size + ((j0 + jj) % page_size)) * dv;
 #pragma unroll
       for (int r = 0; r < ATT_MAX_D / 32; ++r) {
         const int i = lane + 32 * r;
-        if (i < d) acc[r] = fmaf(pj, to_f32(vp[i]), acc[r]);
+        if (i < dv) acc[r] = fmaf(pj, to_f32(vp[i]), acc[r]);
       }
     }
   }
-  T* orow = out + ((size_t)t * nq + h) * d;
+  T* orow = out + ((size_t)t * nq + h) * dv;
   const float inv = (l > 0.f) ? 1.0f / l : 0.f;
 #pragma unroll
   for (int r = 0; r < ATT_MAX_D / 32; ++r) {
     const int i = lane + 32 * r;
-    if (i < d) orow[i] = from_f32<T>(acc[r] * inv);
+    if (i < dv) orow[i] = from_f32<T>(acc[r] * inv);
   }
+}
+
+// keys [pages, nkv, page_size, d], values [pages, nkv, page_size, dv], out [T, nq * dv]
+RLLM_EXPORT int rllm_attention_simt_kv(const void* q, int q_stride, void* out, const void* kcache,
+                                       const void* vcache, int dtype, const int* block_table,
+                                       int max_blocks, const int* positions, const int* token_seq, int T,
+                                       int nq, int nkv, int d, int dv, int page_size, int num_pages, int window,
+                                       float scale, int* err, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || d <= 0 || dv <= 0 || page_size <= 0 || num_pages <= 0 ||
+      max_blocks <= 0 || window < 0)
+    return RLLM_E_BADARG;
+  if (dv > ATT_MAX_D || d > 1024) return RLLM_E_UNSUPPORTED;
+  const bool vec = d % 8 == 0 && q_stride % 8 == 0 && (((uintptr_t)q | (uintptr_t)kcache) & 31) == 0;
+  const long long warps = (long long)T * nq;
+  const unsigned blocks = (unsigned)((warps + ATT_WARPS - 1) / ATT_WARPS);
+  const size_t smem = (size_t)ATT_WARPS * d * sizeof(float);
+#define ATT_GO(VEC_)                                                                                        \
+  RLLM_DISPATCH_DTYPE(dtype, T_,                                                                            \
+    (attention_simt_kernel<T_, VEC_><<<blocks, 32 * ATT_WARPS, smem, stream>>>(                             \
+        (const T_*)q, q_stride, (T_*)out, (const T_*)kcache, (const T_*)vcache, block_table,                \
+        max_blocks, positions, token_seq, T, nq, nkv, d, dv, page_size, num_pages, window, scale, err)))
+  if (vec) ATT_GO(true); else ATT_GO(false);
+#undef ATT_GO
+  RLLM_LAUNCH_CHECK();
+  return 0;
 }
 
 RLLM_EXPORT int rllm_attention_simt(const void* q, int q_stride, void* out, const void* kcache,
@@ -124,19 +156,8 @@ RLLM_EXPORT int rllm_attention_simt(const void* q, int q_stride, void* out, cons
                                     int max_blocks, const int* positions, const int* token_seq, int T,
                                     int nq, int nkv, int d, int page_size, int num_pages, int window,
                                     float scale, int* err, cudaStream_t stream) {
-  if (T <= 0) return 0;
-  if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || d <= 0 || page_size <= 0 || num_pages <= 0 ||
-      max_blocks <= 0 || window < 0)
-    return RLLM_E_BADARG;
-  if (d % 16 != 0 || d > ATT_MAX_D) return RLLM_E_UNSUPPORTED;  // head sizes in steps of 16, to 256
+  if (d % 16 != 0 || d > ATT_MAX_D) return d > 0 ? RLLM_E_UNSUPPORTED : RLLM_E_BADARG;  // head sizes in steps of 16, to 256
   if (q_stride % 8 != 0) return RLLM_E_BADARG;
-  const long long warps = (long long)T * nq;
-  const unsigned blocks = (unsigned)((warps + ATT_WARPS - 1) / ATT_WARPS);
-  const size_t smem = (size_t)ATT_WARPS * d * sizeof(float);
-  RLLM_DISPATCH_DTYPE(dtype, T_,
-    (attention_simt_kernel<T_><<<blocks, 32 * ATT_WARPS, smem, stream>>>(
-        (const T_*)q, q_stride, (T_*)out, (const T_*)kcache, (const T_*)vcache, block_table,
-        max_blocks, positions, token_seq, T, nq, nkv, d, page_size, num_pages, window, scale, err)));
-  RLLM_LAUNCH_CHECK();
-  return 0;
+  return rllm_attention_simt_kv(q, q_stride, out, kcache, vcache, dtype, block_table, max_blocks, positions,
+                                token_seq, T, nq, nkv, d, d, page_size, num_pages, window, scale, err, stream);
 }

@@ -9,34 +9,41 @@
 #include "common.cuh"
 
 // ---------------------------------------------------------------------------
-// embedding: out[t, :] = table[ids[t], :]   (no scaling;
-// crates/rllm-model/src/llama.rs:329-337)
+// embedding: out[c, t, :] = table[ids[t], :] * scale for each of `copies` copies of the
+// residual (the reference does not scale: crates/rllm-model/src/llama.rs:329-337; a
+// design with several residual streams starts them all from the same rows)
 // ---------------------------------------------------------------------------
 template <typename TW>
 __global__ void embedding_kernel(const int* __restrict__ ids, const TW* __restrict__ table,
-                                 float* __restrict__ out, int H, int V, int* __restrict__ err) {
+                                 float* __restrict__ out, int H, int V, float scale, int copies,
+                                 int* __restrict__ err) {
   pdl_wait_on(ids);              // (in a decode graph the token ids come from the kernel directly ahead)
   pdl_launch();
   const int t = blockIdx.x;
   const int id = ids[t];
+  const size_t copy_stride = (size_t)gridDim.x * H;
   float* o = out + (size_t)t * H;
   if (id < 0 || id >= V) {
     if (threadIdx.x == 0) atomicOr(err, 1);
-    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = 0.f;
+    for (int c = 0; c < copies; ++c)
+      for (int i = threadIdx.x; i < H; i += blockDim.x) o[c * copy_stride + i] = 0.f;
     return;
   }
   const TW* row = table + (size_t)id * H;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_f32(row[i]);
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float v = to_f32(row[i]) * scale;
+    for (int c = 0; c < copies; ++c) o[c * copy_stride + i] = v;
+  }
 }
 
 RLLM_EXPORT int rllm_embedding(const int* ids, const void* table, int table_dtype, float* out,
-                               int T, int H, int V, int* err, cudaStream_t stream) {
+                               int T, int H, int V, float scale, int copies, int* err, cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (H <= 0 || V <= 0) return RLLM_E_BADARG;
+  if (H <= 0 || V <= 0 || copies <= 0) return RLLM_E_BADARG;
   int threads = H >= 1024 ? 256 : 128;
   cudaError_t e = cudaErrorInvalidValue;
   RLLM_DISPATCH_DTYPE(table_dtype, TW,
-    (e = rllm_launch_pdl(embedding_kernel<TW>, dim3(T), dim3(threads), 0, stream, ids, (const TW*)table, out, H, V, err)));
+    (e = rllm_launch_pdl(embedding_kernel<TW>, dim3(T), dim3(threads), 0, stream, ids, (const TW*)table, out, H, V, scale, copies, err)));
   return (int)e;
 }
 
@@ -410,6 +417,32 @@ __global__ void silu_mul_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __rest
     op[k] = __floats2bfloat162_rn(gf.x / (1.0f + expf(-gf.x)) * uf.x, gf.y / (1.0f + expf(-gf.y)) * uf.y);
   }
   *(uint4*)(out + idx * 8) = o;
+}
+
+// out[t, i] = act(gu[t, i]) * gu[t, I + i] with act 0: silu, 1: the tanh form of gelu,
+// 0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)))
+template <typename T>
+__global__ void act_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t n, int act) {
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= n) return;
+  const size_t t = idx / I;
+  const int i = (int)(idx - t * I);
+  const float g = to_f32(gu[t * 2 * I + i]);
+  const float u = to_f32(gu[t * 2 * I + I + i]);
+  const float a = act == 1 ? 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)))
+                           : g / (1.0f + expf(-g));
+  out[idx] = from_f32<T>(a * u);
+}
+
+RLLM_EXPORT int rllm_act_mul(const void* gu, void* out, int dtype, int T, int I, int act, cudaStream_t stream) {
+  if (T <= 0 || I <= 0) return 0;
+  if (act != 0 && act != 1) return RLLM_E_BADARG;
+  const size_t n = (size_t)T * I;
+  const unsigned blocks = (unsigned)((n + 255) / 256);
+  RLLM_DISPATCH_DTYPE(dtype, T_,
+    (act_mul_kernel<T_><<<blocks, 256, 0, stream>>>((const T_*)gu, (T_*)out, I, n, act)));
+  RLLM_LAUNCH_CHECK();
+  return 0;
 }
 
 RLLM_EXPORT int rllm_silu_mul(const void* gu, void* out, int dtype, int T, int I, cudaStream_t stream) {

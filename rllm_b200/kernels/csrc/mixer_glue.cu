@@ -1,0 +1,142 @@
+// Small steps around mixers, each one pass over its rows, float32 arithmetic:
+//
+//   head_norm_kv_write   per-head RMS norm of queries (in place) and keys, and the write of
+//                        a token's keys and values into its cache pages; keys and values may
+//                        have different sizes per head; without norm weights it is the bare write
+//   rms_mean             out = (1/n) sum_i rms(x_i) * w_i  over n = 2 inputs of one width
+//                        (branches of a mixer that run side by side)
+//   gated_rmsnorm        out = rms(x) * w * sigmoid(g)     (x float32, g in the activation dtype)
+//
+// rms(x) = x / sqrt(mean(x^2) + eps), eps inside the root.  One warp a head or one block a
+// row; the order of a row's additions depends on its width only.
+#include "common.cuh"
+#include <math.h>
+
+#define HN_WARPS 4
+
+// qkv: T rows of [nq * dk | nkv * dk | nkv * dv] with row stride `stride`.
+template <typename T, typename TW>
+__global__ void __launch_bounds__(32 * HN_WARPS)
+head_norm_kv_write_kernel(T* qkv, int stride, const int* positions, const int* token_seq, const TW* wq, const TW* wk,
+                          float eps, const int* block_table, int max_blocks, T* kcache, T* vcache, int T_tokens, int nq,
+                          int nkv, int dk, int dv, int page_size, int num_pages, int write_kv, int* err) {
+  pdl_wait();
+  pdl_launch();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int heads = nq + 2 * nkv;
+  const long long gw = (long long)blockIdx.x * HN_WARPS + warp;
+  if (gw >= (long long)T_tokens * heads) return;
+  const int t = (int)(gw / heads), h = (int)(gw - (long long)t * heads);
+  T* row = qkv + (size_t)t * stride;
+  T* dst = nullptr;
+  if (h >= nq) {
+    if (!write_kv) return;
+    const int pos = positions[t], s = token_seq[t];
+    const int blk = pos / page_size;
+    const int page = (blk < max_blocks) ? block_table[(size_t)s * max_blocks + blk] : -1;
+    if (page < 0 || page >= num_pages) {
+      if (lane == 0) atomicOr(err, 2);
+      return;
+    }
+    const int kvh = (h - nq) % nkv;
+    dst = (h < nq + nkv) ? kcache + (((size_t)page * nkv + kvh) * page_size + pos % page_size) * dk
+                         : vcache + (((size_t)page * nkv + kvh) * page_size + pos % page_size) * dv;
+  }
+  if (h >= nq + nkv) {                                    // a value head: copied as it is
+    const T* src = row + (size_t)nq * dk + (size_t)nkv * dk + (size_t)(h - nq - nkv) * dv;
+    for (int i = lane; i < dv; i += 32) dst[i] = src[i];
+    return;
+  }
+  T* src = row + (size_t)h * dk;                          // query heads, then key heads: both dk wide
+  const TW* w = (h < nq) ? wq : wk;
+  if (!w) {
+    if (dst) for (int i = lane; i < dk; i += 32) dst[i] = src[i];
+    return;
+  }
+  float ss = 0.f;
+  for (int i = lane; i < dk; i += 32) { const float v = to_f32(src[i]); ss = fmaf(v, v, ss); }
+  ss = warp_sum(ss);
+  const float r = 1.0f / sqrtf(ss / (float)dk + eps);
+  T* o = dst ? dst : src;
+  for (int i = lane; i < dk; i += 32) o[i] = from_f32<T>(to_f32(src[i]) * r * to_f32(w[i]));
+}
+
+RLLM_EXPORT int rllm_head_norm_kv_write(void* qkv, int dtype, int stride, const int* positions, const int* token_seq,
+                                        const void* wq, const void* wk, int w_dtype, float eps, const int* block_table,
+                                        int max_blocks, void* kcache, void* vcache, int T, int nq, int nkv, int dk,
+                                        int dv, int page_size, int num_pages, int write_kv, int* err,
+                                        cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (nq <= 0 || nkv < 0 || dk <= 0 || dv <= 0) return RLLM_E_BADARG;
+  if (write_kv && (page_size <= 0 || num_pages <= 0 || max_blocks <= 0 || !kcache || !vcache)) return RLLM_E_BADARG;
+  const long long warps = (long long)T * (nq + 2 * nkv);
+  const unsigned blocks = (unsigned)((warps + HN_WARPS - 1) / HN_WARPS);
+  RLLM_DISPATCH_DTYPE(dtype, TT, RLLM_DISPATCH_DTYPE(w_dtype, TW,
+    (rllm_launch_pdl(head_norm_kv_write_kernel<TT, TW>, dim3(blocks), dim3(32 * HN_WARPS), (size_t)0, stream, (TT*)qkv,
+                     stride, positions, token_seq, (const TW*)wq, (const TW*)wk, eps, block_table, max_blocks,
+                     (TT*)kcache, (TT*)vcache, T, nq, nkv, dk, dv, page_size, num_pages, write_kv, err))));
+  RLLM_LAUNCH_CHECK();
+  return 0;
+}
+
+// out[r] = 1/2 (rms(a[r]) wa + rms(b[r]) wb)
+template <typename T, typename TW>
+__global__ void __launch_bounds__(256)
+rms_mean2_kernel(const T* a, const T* b, const TW* wa, const TW* wb, T* out, int H, float eps) {
+  __shared__ float red[32];
+  pdl_wait();
+  pdl_launch();
+  const size_t base = (size_t)blockIdx.x * H;
+  float sa = 0.f, sb = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float x = to_f32(a[base + i]), y = to_f32(b[base + i]);
+    sa = fmaf(x, x, sa);
+    sb = fmaf(y, y, sb);
+  }
+  sa = block_sum(sa, red);
+  sb = block_sum(sb, red);
+  const float ra = 1.0f / sqrtf(sa / (float)H + eps), rb = 1.0f / sqrtf(sb / (float)H + eps);
+  for (int i = threadIdx.x; i < H; i += blockDim.x)
+    out[base + i] = from_f32<T>(0.5f * (to_f32(a[base + i]) * ra * to_f32(wa[i]) + to_f32(b[base + i]) * rb * to_f32(wb[i])));
+}
+
+RLLM_EXPORT int rllm_rms_mean2(const void* a, const void* b, const void* wa, const void* wb, int w_dtype, void* out,
+                               int dtype, int T, int H, float eps, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (H <= 0) return RLLM_E_BADARG;
+  RLLM_DISPATCH_DTYPE(dtype, TT, RLLM_DISPATCH_DTYPE(w_dtype, TW,
+    (rllm_launch_pdl(rms_mean2_kernel<TT, TW>, dim3(T), dim3(256), (size_t)0, stream, (const TT*)a, (const TT*)b,
+                     (const TW*)wa, (const TW*)wb, (TT*)out, H, eps))));
+  RLLM_LAUNCH_CHECK();
+  return 0;
+}
+
+// out[r] = rms(x[r]) * w * sigmoid(g[r]);  x float32 [T, H], g rows with stride g_stride
+template <typename T, typename TW>
+__global__ void __launch_bounds__(256)
+gated_rmsnorm_kernel(const float* x, const T* g, int g_stride, const TW* w, T* out, int H, float eps) {
+  __shared__ float red[32];
+  pdl_wait();
+  pdl_launch();
+  const size_t base = (size_t)blockIdx.x * H;
+  const T* gr = g + (size_t)blockIdx.x * g_stride;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) { const float v = x[base + i]; ss = fmaf(v, v, ss); }
+  ss = block_sum(ss, red);
+  const float r = 1.0f / sqrtf(ss / (float)H + eps);
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float gate = 1.0f / (1.0f + expf(-to_f32(gr[i])));
+    out[base + i] = from_f32<T>(x[base + i] * r * to_f32(w[i]) * gate);
+  }
+}
+
+RLLM_EXPORT int rllm_gated_rmsnorm(const float* x, const void* g, int g_stride, const void* w, int w_dtype, void* out,
+                                   int dtype, int T, int H, float eps, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (H <= 0) return RLLM_E_BADARG;
+  RLLM_DISPATCH_DTYPE(dtype, TT, RLLM_DISPATCH_DTYPE(w_dtype, TW,
+    (rllm_launch_pdl(gated_rmsnorm_kernel<TT, TW>, dim3(T), dim3(256), (size_t)0, stream, x, (const TT*)g, g_stride,
+                     (const TW*)w, (TT*)out, H, eps))));
+  RLLM_LAUNCH_CHECK();
+  return 0;
+}

@@ -5,8 +5,9 @@
 //             pairs in that order, and a list of row tiles (expert, first row), all on
 //             the device, so that no size is read back to the host.
 //   gate_up:  per expert, y = act(W_gate h, W_up h) for its rows, with
-//             act(g, u) = g' sigmoid(alpha g') (u' + 1), g' = min(g, limit),
-//             u' = clamp(u, -limit, limit)  (alpha and limit are arguments).
+//             act(g, u) = g' sigmoid(alpha g') (u' + shift), g' = min(g, limit),
+//             u' = clamp(u, -limit, limit)  (alpha, limit and shift are arguments; alpha 1,
+//             no limit and shift 0 give silu(g) u).
 //   down:     per expert, W_down y, written to the pair's own row; the weighted sum
 //             over a token's pairs is taken by the kernel that reads the result, in
 //             the order of the choices.
@@ -115,6 +116,60 @@ moe_choose_kernel(const float* logits, int* ids, float* weights,
   }
 }
 
+// Scores that do not compete: s = sigmoid(z) per expert.  The `top` experts with the largest s + bias are
+// chosen (bias [E] may be absent; lowest index among equals); their weights are s * scale, the bias left out.
+__global__ void __launch_bounds__(32 * ROUTE_WARPS)
+moe_choose_sigmoid_kernel(const float* logits, const float* bias, float scale, int* ids, float* weights,
+                          int T_tokens, int E, int top) {
+  pdl_wait();
+  pdl_launch();
+  extern __shared__ float zs[];   // [ROUTE_WARPS][2 E]: choice scores, then the scores themselves
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t = blockIdx.x * ROUTE_WARPS + warp;
+  if (t >= T_tokens) return;
+  float* z = zs + warp * 2 * E;
+  float* sc = z + E;
+  for (int e = lane; e < E; e += 32) {
+    float v = 1.0f / (1.0f + expf(-logits[(size_t)t * E + e]));
+    if (v != v) v = 0.f;                   // a NaN score still leaves an expert index inside the range
+    sc[e] = v;
+    z[e] = v + (bias ? bias[e] : 0.f);
+  }
+  __syncwarp();
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      const float v = z[e];
+      if (v > best || (bi == 0x7fffffff && v > -INFINITY)) { best = v; bi = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+    }
+    if (bi >= E) bi = 0;
+    if (lane == 0) {
+      ids[(size_t)t * top + k] = bi;
+      weights[(size_t)t * top + k] = sc[bi] * scale;
+      z[bi] = -INFINITY;
+    }
+    __syncwarp();
+  }
+}
+
+RLLM_EXPORT int rllm_moe_choose_sigmoid(const float* logits, const float* bias, float scale, int* ids, float* weights,
+                                        int T, int E, int top, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (E <= 0 || top <= 0 || top > E || E > 2048) return RLLM_E_BADARG;
+  const unsigned blocks = (unsigned)((T + ROUTE_WARPS - 1) / ROUTE_WARPS);
+  rllm_launch_pdl(moe_choose_sigmoid_kernel, dim3(blocks), dim3(32 * ROUTE_WARPS),
+                  (size_t)((size_t)ROUTE_WARPS * 2 * E * sizeof(float)), stream, logits, bias, scale, ids, weights, T, E, top);
+  RLLM_LAUNCH_CHECK();
+  return 0;
+}
+
 RLLM_EXPORT int rllm_moe_choose(const float* logits, int* ids, float* weights, int T, int E, int top,
                                 cudaStream_t stream) {
   if (T <= 0) return 0;
@@ -196,7 +251,7 @@ __global__ void __launch_bounds__(TG_THREADS)
 moe_gate_up_kernel(const T* h, const T* w, T* y,
                    const int* offsets, const int* sorted,
                    const int* tile_expert, const int* tile_row0,
-                   const int* meta, int H, int F, int top, float limit, float alpha) {
+                   const int* meta, int H, int F, int top, float limit, float alpha, float up_shift) {
   pdl_wait();
   pdl_launch();
   __shared__ TileGemmSmem<BM> sm;
@@ -223,7 +278,7 @@ moe_gate_up_kernel(const T* h, const T* w, T* y,
       const int n = n0 + tn + j;
       if (n >= F) continue;
       const float gg = fminf(g[i][j], limit), uu = fminf(fmaxf(u[i][j], -limit), limit);
-      y[(size_t)r * F + n] = from_f32<T>(gg * (1.0f / (1.0f + expf(-alpha * gg))) * (uu + 1.0f));
+      y[(size_t)r * F + n] = from_f32<T>(gg * (1.0f / (1.0f + expf(-alpha * gg))) * (uu + up_shift));
     }
   }
 }
@@ -269,7 +324,7 @@ __global__ void __launch_bounds__(TGM_THREADS)
 moe_gate_up_mma_kernel(const bf16* h, const bf16* w, bf16* y,
                        const int* offsets, const int* sorted,
                        const int* tile_expert, const int* tile_row0,
-                       const int* meta, int H, int F, int top, float limit, float alpha) {
+                       const int* meta, int H, int F, int top, float limit, float alpha, float up_shift) {
   pdl_wait();
   pdl_launch();
   MmaTileSmem<BM, 2>& sm = tgm_smem<BM, 2>();
@@ -295,7 +350,7 @@ moe_gate_up_mma_kernel(const bf16* h, const bf16* w, bf16* y,
       const int r = r0 + tr, n = n0 + tc;
       if (r >= rend || n >= F) continue;
       const float gg = fminf(acc[0][nt][i], limit), uu = fminf(fmaxf(acc[1][nt][i], -limit), limit);
-      y[(size_t)r * F + n] = __float2bfloat16_rn(gg * (1.0f / (1.0f + expf(-alpha * gg))) * (uu + 1.0f));
+      y[(size_t)r * F + n] = __float2bfloat16_rn(gg * (1.0f / (1.0f + expf(-alpha * gg))) * (uu + up_shift));
     }
 }
 
@@ -332,10 +387,11 @@ moe_down_mma_kernel(const bf16* y, const bf16* w, bf16* out,
     }
 }
 
-// out[t, :] = sum_k c[t, k] y[t * K + k, :], the k terms in order
+// out[t, :] = sum_k c[t, k] y[t * K + k, :], the k terms in order; then, if `extra` is given,
+// + sigmoid(extra_gate[t]) * extra[t, :]  (a part that runs for every token, gated by one number a token)
 template <typename T>
 __global__ void weighted_slot_sum_kernel(const T* y, const float* c, T* out,
-                                         int slots, int H, long long total) {
+                                         int slots, int H, long long total, const T* extra, const float* extra_gate) {
   pdl_wait();
   pdl_launch();
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -344,17 +400,18 @@ __global__ void weighted_slot_sum_kernel(const T* y, const float* c, T* out,
   const int i = (int)(idx - t * H);
   float v = 0.f;
   for (int k = 0; k < slots; ++k) v = fmaf(c[t * slots + k], to_f32(y[((size_t)t * slots + k) * H + i]), v);
+  if (extra) v = fmaf(extra_gate ? 1.0f / (1.0f + expf(-extra_gate[t])) : 1.0f, to_f32(extra[idx]), v);
   out[idx] = from_f32<T>(v);
 }
 
 RLLM_EXPORT int rllm_weighted_slot_sum(const void* y, const float* c, void* out, int T, int slots, int H,
-                                       int dtype, cudaStream_t stream) {
+                                       const void* extra, const float* extra_gate, int dtype, cudaStream_t stream) {
   const long long total = (long long)T * H;
   if (total <= 0) return 0;
   if (slots <= 0) return RLLM_E_BADARG;
   const unsigned blocks = (unsigned)((total + 255) / 256);
   RLLM_DISPATCH_DTYPE(dtype, TT, (rllm_launch_pdl(weighted_slot_sum_kernel<TT>, dim3(blocks), dim3(256), (size_t)(0), stream, 
-      (const TT*)y, c, (TT*)out, slots, H, total)));
+      (const TT*)y, c, (TT*)out, slots, H, total, (const TT*)extra, extra_gate)));
   RLLM_LAUNCH_CHECK();
   return 0;
 }
@@ -362,7 +419,7 @@ RLLM_EXPORT int rllm_weighted_slot_sum(const void* y, const float* c, void* out,
 RLLM_EXPORT int rllm_moe_experts(const void* h, const void* w_gate_up, const void* w_down, void* y, void* out,
                                  const int* offsets, const int* sorted, const int* tile_expert,
                                  const int* tile_row0, const int* meta, int max_tiles, int bm, int H, int F,
-                                 int top, float limit, float alpha, int dtype, cudaStream_t stream) {
+                                 int top, float limit, float alpha, float up_shift, int dtype, cudaStream_t stream) {
   if (max_tiles <= 0) return 0;
   if (H <= 0 || F <= 0 || top <= 0 || (bm != 16 && bm != 64)) return RLLM_E_BADARG;
   if (max_tiles > 65535) return RLLM_E_UNSUPPORTED;
@@ -374,7 +431,7 @@ RLLM_EXPORT int rllm_moe_experts(const void* h, const void* w_gate_up, const voi
   do {                                                                                                       \
     tgm_allow_smem<decltype(&moe_gate_up_mma_kernel<BM_>), BM_, 2>(moe_gate_up_mma_kernel<BM_>);             \
     rllm_launch_pdl(moe_gate_up_mma_kernel<BM_>, dim3(g1), dim3(TGM_THREADS), (size_t)(sizeof(MmaTileSmem<BM_, 2>)), stream, (const bf16*)h, (const bf16*)w_gate_up,      \
-        (bf16*)y, offsets, sorted, tile_expert, tile_row0, meta, H, F, top, limit, alpha);                   \
+        (bf16*)y, offsets, sorted, tile_expert, tile_row0, meta, H, F, top, limit, alpha, up_shift);                   \
     tgm_allow_smem<decltype(&moe_down_mma_kernel<BM_>), BM_, 1>(moe_down_mma_kernel<BM_>);                   \
     rllm_launch_pdl(moe_down_mma_kernel<BM_>, dim3(g2), dim3(TGM_THREADS), (size_t)(sizeof(MmaTileSmem<BM_, 1>)), stream, (const bf16*)y, (const bf16*)w_down, (bf16*)out, \
         offsets, sorted, tile_expert, tile_row0, meta, H, F);                                                \
@@ -387,7 +444,7 @@ RLLM_EXPORT int rllm_moe_experts(const void* h, const void* w_gate_up, const voi
 #define MOE_LAUNCH(T_, BM_)                                                                                  \
   do {                                                                                                       \
     rllm_launch_pdl(moe_gate_up_kernel<T_, BM_>, dim3(g1), dim3(TG_THREADS), (size_t)(0), stream, (const T_*)h, (const T_*)w_gate_up, (T_*)y,    \
-        offsets, sorted, tile_expert, tile_row0, meta, H, F, top, limit, alpha);                             \
+        offsets, sorted, tile_expert, tile_row0, meta, H, F, top, limit, alpha, up_shift);                             \
     rllm_launch_pdl(moe_down_kernel<T_, BM_>, dim3(g2), dim3(TG_THREADS), (size_t)(0), stream, (const T_*)y, (const T_*)w_down, (T_*)out, offsets, \
         sorted, tile_expert, tile_row0, meta, H, F);                                                         \
   } while (0)

@@ -59,14 +59,17 @@ def _contig(t: torch.Tensor, name: str) -> None:
 
 
 # ---------------------------------------------------------------------------
-def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, err: torch.Tensor) -> None:
-    """out[t] = table[ids[t]] as float32; ids int32 [T], out float32 [T, H]."""
+def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, err: torch.Tensor,
+              scale: float = 1.0) -> None:
+    """out[t] = table[ids[t]] * scale as float32; ids int32 [T], out float32 [T, H], or [C, T, H]: C copies."""
     lib = build.load_library("elementwise")
     T, (V, H) = ids.numel(), table.shape
-    assert ids.dtype is torch.int32 and out.dtype is torch.float32 and out.shape == (T, H)
+    copies = out.shape[0] if out.dim() == 3 else 1
+    assert ids.dtype is torch.int32 and out.dtype is torch.float32 and out.shape[-2:] == (T, H)
     _contig(table, "table"); _contig(out, "out")
     _check(lib.rllm_embedding(_ptr(ids), _ptr(table), c_int(dtype_code(table.dtype)), _ptr(out),
-                              c_int(T), c_int(H), c_int(V), _ptr(err), _stream()), "embedding")
+                              c_int(T), c_int(H), c_int(V), c_float(scale), c_int(copies), _ptr(err), _stream()),
+           "embedding")
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
@@ -890,9 +893,10 @@ def moe_choose(logits: torch.Tensor, top: int):
 
 
 def moe_experts(h: torch.Tensor, ids: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, limit: float,
-                alpha: float) -> torch.Tensor:
+                alpha: float, up_shift: float = 1.0) -> torch.Tensor:
     """out [T * top, H]: row t * top + k is expert ids[t, k] applied to h[t]:
-    W_down (g' sigmoid(alpha g') (u' + 1)), g' = min(W_gate h, limit), u' = clamp(W_up h, +-limit).
+    W_down (g' sigmoid(alpha g') (u' + up_shift)), g' = min(W_gate h, limit), u' = clamp(W_up h, +-limit)
+    (limit inf, alpha 1, up_shift 0: silu(W_gate h) * W_up h).
     w_gate_up [E, 2 F, H] (gate rows, then up rows), w_down [E, H, F]."""
     lib = build.load_library("moe")
     T, H = h.shape
@@ -916,16 +920,300 @@ def moe_experts(h: torch.Tensor, ids: torch.Tensor, w_gate_up: torch.Tensor, w_d
     _check(lib.rllm_moe_experts(_ptr(h), _ptr(w_gate_up), _ptr(w_down), _ptr(y), _ptr(out), _ptr(offsets),
                                 _ptr(sorted_pairs), _ptr(tile_expert), _ptr(tile_row0), _ptr(m_tiles),
                                 c_int(max_tiles), c_int(bm), c_int(H), c_int(F), c_int(top), c_float(limit),
-                                c_float(alpha), c_int(dtype_code(h.dtype)), _stream()), "moe_experts")
+                                c_float(alpha), c_float(up_shift), c_int(dtype_code(h.dtype)), _stream()),
+           "moe_experts")
     return out
 
 
-def weighted_slot_sum(y: torch.Tensor, coeff: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t] = sum_k coeff[t, k] * y[t * K + k]; y [T * K, H], coeff float32 [T, K], out [T, H]."""
+def weighted_slot_sum(y: torch.Tensor, coeff: torch.Tensor, out: torch.Tensor, extra: Optional[torch.Tensor] = None,
+                      extra_gate: Optional[torch.Tensor] = None) -> None:
+    """out[t] = sum_k coeff[t, k] * y[t * K + k] (+ sigmoid(extra_gate[t]) * extra[t]); y [T * K, H], coeff
+    float32 [T, K], out and extra [T, H], extra_gate float32 [T] (absent: the extra row is added as it is)."""
     lib = build.load_library("moe")
     T, H = out.shape
     K = coeff.shape[1]
     assert y.shape == (T * K, H) and coeff.shape == (T, K) and coeff.dtype is torch.float32 and y.dtype is out.dtype
     _contig(y, "y"); _contig(coeff, "coeff"); _contig(out, "out")
-    _check(lib.rllm_weighted_slot_sum(_ptr(y), _ptr(coeff), _ptr(out), c_int(T), c_int(K), c_int(H),
+    if extra is not None:
+        assert extra.shape == out.shape and extra.dtype is out.dtype
+        _contig(extra, "extra")
+        if extra_gate is not None:
+            assert extra_gate.dtype is torch.float32 and extra_gate.numel() == T and extra_gate.is_contiguous()
+    _check(lib.rllm_weighted_slot_sum(_ptr(y), _ptr(coeff), _ptr(out), c_int(T), c_int(K), c_int(H), _ptr(extra),
+                                      _ptr(extra_gate if extra is not None else None),
                                       c_int(dtype_code(out.dtype)), _stream()), "weighted_slot_sum")
+
+
+def moe_choose_sigmoid(logits: torch.Tensor, top: int, bias: Optional[torch.Tensor], scale: float):
+    """(ids int32 [T, top], weights float32 [T, top]) from float32 router logits [T, E]: s = sigmoid(z); the
+    ``top`` experts with the largest s + bias (float32 [E] or None; lowest index among equals), in falling
+    order; weights s * scale without the bias."""
+    lib = build.load_library("moe")
+    T, E = logits.shape
+    assert logits.dtype is torch.float32
+    _contig(logits, "logits")
+    if bias is not None:
+        assert bias.dtype is torch.float32 and bias.numel() == E and bias.is_contiguous()
+    ids = torch.empty((T, top), dtype=torch.int32, device=logits.device)
+    weights = torch.empty((T, top), dtype=torch.float32, device=logits.device)
+    _check(lib.rllm_moe_choose_sigmoid(_ptr(logits), _ptr(bias), c_float(scale), _ptr(ids), _ptr(weights), c_int(T),
+                                       c_int(E), c_int(top), _stream()), "moe_choose_sigmoid")
+    return ids, weights
+
+
+ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+
+def act_mul(gate_up: torch.Tensor, out: torch.Tensor, activation: str) -> None:
+    """out[t, i] = act(gate_up[t, i]) * gate_up[t, I + i]; act "silu" or "gelu_tanh"."""
+    lib = build.load_library("elementwise")
+    T, I = out.shape
+    assert gate_up.shape == (T, 2 * I) and gate_up.dtype is out.dtype
+    _contig(gate_up, "gate_up"); _contig(out, "out")
+    _check(lib.rllm_act_mul(_ptr(gate_up), _ptr(out), c_int(dtype_code(out.dtype)), c_int(T), c_int(I),
+                            c_int(ACTIVATIONS[activation]), _stream()), "act_mul")
+
+
+# ---------------------------------------------------------------------------
+# several residual streams (hyper_streams.cu)
+# ---------------------------------------------------------------------------
+HS_MAX_STREAMS = 8
+
+
+def _norm_args(norm):
+    """(alpha, weight, shift) of a dynamic-tanh norm, or three Nones."""
+    if norm is None:
+        return None, None, None
+    alpha, w, c = norm
+    assert alpha.dtype is torch.float32 and alpha.numel() == 1 and w.dtype is c.dtype and w.shape == c.shape
+    _contig(w, "norm weight"); _contig(c, "norm shift")
+    return alpha, w, c
+
+
+def streams_read(xs: torch.Tensor, coeff: Optional[torch.Tensor], norm, out_dtype: torch.dtype,
+                 rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[r] = n(sum_s coeff[s] * xs[s, row(r)]); xs float32 [S, T, H]; coeff float32 [S] (None: ones);
+    ``norm`` = (alpha float32 [1], weight [H], shift [H]) applies n(u) = tanh(alpha u) * weight + shift and
+    rounds to ``out_dtype``; None: out is the float32 sum.  ``rows`` int32 [R] picks rows."""
+    lib = build.load_library("hyper_streams")
+    S, T, H = xs.shape
+    assert xs.dtype is torch.float32 and S <= HS_MAX_STREAMS
+    _contig(xs, "xs")
+    alpha, w, c = _norm_args(norm)
+    if coeff is not None:
+        assert coeff.dtype is torch.float32 and coeff.numel() == S and coeff.is_contiguous()
+    R = T if rows is None else rows.numel()
+    if rows is not None:
+        assert rows.dtype is torch.int32
+    od = out_dtype if w is not None else torch.float32
+    out = torch.empty((R, H), dtype=od, device=xs.device)
+    _check(lib.rllm_hs_read(_ptr(xs), _ptr(coeff), _ptr(rows), _ptr(alpha), _ptr(w), _ptr(c),
+                            c_int(dtype_code(w.dtype) if w is not None else DT_F32), _ptr(out), c_int(dtype_code(od)),
+                            c_int(S), c_longlong(T), c_int(R), c_int(H), _stream()), "streams_read")
+    return out
+
+
+def streams_write(xs: torch.Tensor, y: torch.Tensor, scale: Optional[torch.Tensor], mix: torch.Tensor,
+                  write: torch.Tensor, next_read: Optional[torch.Tensor] = None, norm=None,
+                  sum_out: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """xs (float32 [S, T, H], in place): x_t <- sum_s mix[s, t] x_s + write[t] * (scale * y), all streams from
+    the old ones; y [T, H]; scale [H] or None; mix float32 [S, S] (from, to); write float32 [S].  With
+    ``next_read`` (float32 [S]) the next read comes back too: n(sum_t next_read[t] x_t) with ``norm`` as in
+    ``streams_read`` (in y's dtype), or the float32 sum without one.  ``sum_out`` float32 [T, H], if given,
+    receives the plain sum of the new streams."""
+    lib = build.load_library("hyper_streams")
+    S, T, H = xs.shape
+    assert xs.dtype is torch.float32 and S <= HS_MAX_STREAMS and y.shape == (T, H)
+    assert mix.dtype is torch.float32 and mix.shape == (S, S) and write.dtype is torch.float32 and write.numel() == S
+    _contig(xs, "xs"); _contig(y, "y"); _contig(mix, "mix"); _contig(write, "write")
+    alpha, w, c = _norm_args(norm)
+    wd = w.dtype if w is not None else (scale.dtype if scale is not None else torch.float32)
+    if scale is not None:
+        assert scale.numel() == H and scale.is_contiguous() and scale.dtype is wd
+    out = None
+    if next_read is not None:
+        assert next_read.dtype is torch.float32 and next_read.numel() == S and next_read.is_contiguous()
+        out = torch.empty((T, H), dtype=y.dtype if w is not None else torch.float32, device=xs.device)
+    if sum_out is not None:
+        assert sum_out.dtype is torch.float32 and sum_out.shape == (T, H) and sum_out.is_contiguous()
+    _check(lib.rllm_hs_write(_ptr(xs), _ptr(y), c_int(dtype_code(y.dtype)), _ptr(scale), _ptr(mix), _ptr(write),
+                             _ptr(next_read), _ptr(alpha), _ptr(w), _ptr(c), c_int(dtype_code(wd)), _ptr(out),
+                             _ptr(sum_out), c_int(S), c_longlong(T), c_int(H), _stream()), "streams_write")
+    return out
+
+
+def dyt(x: torch.Tensor, alpha: torch.Tensor, weight: torch.Tensor, shift: torch.Tensor, out: torch.Tensor,
+        delta: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None, writeback: bool = False) -> None:
+    """out = tanh(alpha * (x [+ delta])) * weight + shift; x float32 [., H]; the arguments of ``rmsnorm``."""
+    lib = build.load_library("hyper_streams")
+    H, R = x.shape[-1], out.shape[0]
+    assert x.dtype is torch.float32 and alpha.dtype is torch.float32 and weight.dtype is shift.dtype
+    _contig(x, "x"); _contig(out, "out")
+    if delta is not None:
+        assert delta.dtype is out.dtype and delta.shape == x.shape
+        _contig(delta, "delta")
+    if rows is not None:
+        assert rows.dtype is torch.int32 and rows.numel() == R
+    _check(lib.rllm_dyt(_ptr(x), _ptr(delta), _ptr(rows), _ptr(alpha), _ptr(weight), _ptr(shift),
+                        c_int(dtype_code(weight.dtype)), _ptr(out), c_int(dtype_code(out.dtype)), c_int(R), c_int(H),
+                        c_int(1 if writeback else 0), _stream()), "dyt")
+
+
+# ---------------------------------------------------------------------------
+# steps around mixers (mixer_glue.cu)
+# ---------------------------------------------------------------------------
+def head_norm_kv_write(qkv: torch.Tensor, positions: torch.Tensor, token_seq: torch.Tensor,
+                       q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
+                       block_table: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, nq: int, nkv: int,
+                       dk: int, dv: int, err: torch.Tensor, write_kv: bool = True) -> None:
+    """qkv [T, nq dk + nkv dk + nkv dv]: every query head (in place) and key head is divided by its root mean
+    square and multiplied by the weight [dk] (None: left as it is); keys and values go to the token's place in
+    kcache [pages, nkv, page, dk] and vcache [pages, nkv, page, dv]."""
+    lib = build.load_library("mixer_glue")
+    T = qkv.shape[0]
+    assert qkv.shape[1] == nq * dk + nkv * (dk + dv) and qkv.stride(1) == 1
+    wd = q_weight.dtype if q_weight is not None else torch.float32
+    if q_weight is not None:
+        assert k_weight is not None and k_weight.dtype is wd and q_weight.numel() == dk and k_weight.numel() == dk
+    if write_kv:
+        assert kcache.dtype is qkv.dtype and vcache.dtype is qkv.dtype and kcache.shape[3] == dk and vcache.shape[3] == dv
+        _contig(kcache, "kcache"); _contig(vcache, "vcache"); _contig(block_table, "block_table")
+        pages, page_size, max_blocks = kcache.shape[0], kcache.shape[2], block_table.shape[1]
+    else:
+        pages = page_size = max_blocks = 0
+    _check(lib.rllm_head_norm_kv_write(_ptr(qkv), c_int(dtype_code(qkv.dtype)), c_int(qkv.stride(0)), _ptr(positions),
+                                       _ptr(token_seq), _ptr(q_weight), _ptr(k_weight), c_int(dtype_code(wd)),
+                                       c_float(eps), _ptr(block_table), c_int(max_blocks),
+                                       _ptr(kcache if write_kv else None), _ptr(vcache if write_kv else None),
+                                       c_int(T), c_int(nq), c_int(nkv if write_kv else 0), c_int(dk), c_int(dv),
+                                       c_int(page_size), c_int(pages), c_int(1 if write_kv else 0), _ptr(err),
+                                       _stream()), "head_norm_kv_write")
+
+
+def attention_simt_kv(q: torch.Tensor, q_stride: int, out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
+                      block_table: torch.Tensor, positions: torch.Tensor, token_seq: torch.Tensor, nq: int, nkv: int,
+                      window: int, scale: float, err: torch.Tensor) -> None:
+    """``attention_simt`` where keys [pages, nkv, page, dk] and values [pages, nkv, page, dv] have sizes of their
+    own: q rows of nq * dk, out [T, nq * dv]; any dk, dv up to 256."""
+    lib = build.load_library("attention_simt")
+    T, dk, dv = out.shape[0], kcache.shape[3], vcache.shape[3]
+    _contig(out, "out"); _contig(kcache, "kcache"); _contig(vcache, "vcache"); _contig(block_table, "block_table")
+    assert kcache.dtype is q.dtype and vcache.dtype is q.dtype and out.dtype is q.dtype and out.shape[1] == nq * dv
+    _check(lib.rllm_attention_simt_kv(_ptr(q), c_int(q_stride), _ptr(out), _ptr(kcache), _ptr(vcache),
+                                      c_int(dtype_code(q.dtype)), _ptr(block_table), c_int(block_table.shape[1]),
+                                      _ptr(positions), _ptr(token_seq), c_int(T), c_int(nq), c_int(nkv), c_int(dk),
+                                      c_int(dv), c_int(kcache.shape[2]), c_int(kcache.shape[0]), c_int(window),
+                                      c_float(scale), _ptr(err), _stream()), "attention_simt_kv")
+
+
+def rms_mean2(a: torch.Tensor, b: torch.Tensor, wa: torch.Tensor, wb: torch.Tensor, eps: float) -> torch.Tensor:
+    """(rms(a) * wa + rms(b) * wb) / 2 row by row, rms(x) = x / sqrt(mean(x^2) + eps); a, b [T, H]."""
+    lib = build.load_library("mixer_glue")
+    T, H = a.shape
+    assert b.shape == a.shape and b.dtype is a.dtype and wa.dtype is wb.dtype and wa.numel() == H and wb.numel() == H
+    _contig(a, "a"); _contig(b, "b"); _contig(wa, "wa"); _contig(wb, "wb")
+    out = torch.empty_like(a)
+    _check(lib.rllm_rms_mean2(_ptr(a), _ptr(b), _ptr(wa), _ptr(wb), c_int(dtype_code(wa.dtype)), _ptr(out),
+                              c_int(dtype_code(a.dtype)), c_int(T), c_int(H), c_float(eps), _stream()), "rms_mean2")
+    return out
+
+
+def gated_rmsnorm(x: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float,
+                  out_dtype: torch.dtype) -> torch.Tensor:
+    """rms(x) * weight * sigmoid(gate); x float32 [T, H]; gate [T, H] (a column slice of a wider tensor will do)."""
+    lib = build.load_library("mixer_glue")
+    T, H = x.shape
+    assert x.dtype is torch.float32 and gate.shape == (T, H) and gate.stride(1) == 1 and gate.dtype is out_dtype
+    _contig(x, "x"); _contig(weight, "weight")
+    out = torch.empty((T, H), dtype=out_dtype, device=x.device)
+    _check(lib.rllm_gated_rmsnorm(_ptr(x), _ptr(gate), c_int(gate.stride(0)), _ptr(weight),
+                                  c_int(dtype_code(weight.dtype)), _ptr(out), c_int(dtype_code(out_dtype)), c_int(T),
+                                  c_int(H), c_float(eps), _stream()), "gated_rmsnorm")
+    return out
+
+
+# ---------------------------------------------------------------------------
+# recurrences with a state per request (lightning.cu, selective_scan.cu)
+# ---------------------------------------------------------------------------
+SCAN_CHUNKED_FROM = 129       # portions from this many tokens on are scanned as chunks side by side
+
+
+def _chunks_for(lib_chunk: int, max_q_len: int, num_seqs: int) -> int:
+    if max_q_len < SCAN_CHUNKED_FROM:
+        return 0
+    chunks = -(-max_q_len // lib_chunk)
+    return chunks if num_seqs * chunks <= 65535 else 0
+
+
+def lightning_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor, state: torch.Tensor,
+                   q_start: torch.Tensor, slots: torch.Tensor, num_seqs: int, err: torch.Tensor,
+                   max_q_len: int = 1) -> torch.Tensor:
+    """Linear attention with a decay per head.  q, k [T, heads * d] and v [T, heads * dv] are column slices of
+    one tensor (the projections before their silu); state float32 [slots, heads, d, dv], updated in place;
+    returns o float32 [T, heads * dv]."""
+    lib = build.load_library("lightning")
+    heads, d, dv = state.shape[1:]
+    T = q.shape[0]
+    assert q.shape == (T, heads * d) and k.shape == q.shape and v.shape == (T, heads * dv)
+    assert q.stride(0) == k.stride(0) == v.stride(0) and q.stride(1) == k.stride(1) == v.stride(1) == 1
+    assert q.dtype is k.dtype is v.dtype and state.dtype is torch.float32 and decay.dtype is torch.float32
+    assert decay.numel() == heads
+    _contig(state, "state")
+    out = torch.empty((T, heads * dv), dtype=torch.float32, device=q.device)
+    chunks = _chunks_for(int(lib.rllm_lightning_chunk()), max_q_len, num_seqs)
+    work = torch.empty(num_seqs * chunks * heads * d * dv, dtype=torch.float32, device=q.device) if chunks else None
+    _check(lib.rllm_lightning_scan(_ptr(q), _ptr(k), _ptr(v), c_int(q.stride(0)), c_int(dtype_code(q.dtype)),
+                                   _ptr(decay), _ptr(state), _ptr(work), _ptr(q_start), _ptr(slots),
+                                   c_int(state.shape[0]), c_int(num_seqs), c_int(chunks), _ptr(out), c_int(heads),
+                                   c_int(d), c_int(dv), _ptr(err), _stream()), "lightning_scan")
+    return out
+
+
+def causal_conv(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, tail: torch.Tensor,
+                q_start: torch.Tensor, token_seq: torch.Tensor, slots: torch.Tensor, num_seqs: int,
+                any_long: bool, err: torch.Tensor) -> torch.Tensor:
+    """silu(bias + causal convolution per channel); x [T, E] (a column slice will do); weight [E, taps], the
+    last column the current token's; tail float32 [slots, taps - 1, E]: a request's last inputs, read for the
+    places before this step and moved on.  ``any_long``: some sequence brings more than one token."""
+    lib = build.load_library("selective_scan")
+    T, E = x.shape
+    taps = weight.shape[1]
+    assert weight.shape == (E, taps) and bias.numel() == E and weight.dtype is bias.dtype and x.stride(1) == 1
+    assert tail.dtype is torch.float32 and tuple(tail.shape[1:]) == (max(taps - 1, 0), E)
+    _contig(weight, "weight"); _contig(bias, "bias"); _contig(tail, "tail")
+    out = torch.empty((T, E), dtype=x.dtype, device=x.device)
+    _check(lib.rllm_causal_conv(_ptr(x), c_int(x.stride(0)), c_int(dtype_code(x.dtype)), _ptr(weight), _ptr(bias),
+                                c_int(dtype_code(weight.dtype)), _ptr(tail), _ptr(q_start), _ptr(token_seq),
+                                _ptr(slots), c_int(tail.shape[0]), c_int(num_seqs), c_int(1 if any_long else 0),
+                                _ptr(out), c_int(T), c_int(E), c_int(taps), _ptr(err), _stream()), "causal_conv")
+    return out
+
+
+def selective_scan(xc: torch.Tensor, dt_raw: torch.Tensor, dt_bias: torch.Tensor, bc: torch.Tensor, b_off: int,
+                   c_off: int, a_log: torch.Tensor, dskip: torch.Tensor, z: torch.Tensor, state: torch.Tensor,
+                   q_start: torch.Tensor, slots: torch.Tensor, num_seqs: int, err: torch.Tensor,
+                   max_q_len: int = 1) -> torch.Tensor:
+    """The selective recurrence.  xc [T, E]: the convolution's output; dt_raw float32 [T, E]: the step
+    projection before bias and softplus; bc [T, .]: B at columns b_off .. + N, C at c_off .. + N; a_log [E, N];
+    dskip [E]; z [T, E] (a column slice will do); state float32 [slots, N, E], updated in place.  Returns
+    (sum_n S C + dskip xc) * silu(z) as [T, E] in xc's dtype."""
+    lib = build.load_library("selective_scan")
+    T, E = xc.shape
+    N = state.shape[1]
+    assert state.dtype is torch.float32 and state.shape[2] == E and dt_raw.dtype is torch.float32
+    assert dt_raw.shape == (T, E) and a_log.shape == (E, N) and dskip.numel() == E and dt_bias.numel() == E
+    assert a_log.dtype is dskip.dtype is dt_bias.dtype and bc.dtype is xc.dtype and z.dtype is xc.dtype
+    assert bc.stride(1) == 1 and z.stride(1) == 1 and z.shape == (T, E)
+    assert 0 <= b_off and b_off + N <= bc.shape[1] and 0 <= c_off and c_off + N <= bc.shape[1]
+    _contig(xc, "xc"); _contig(dt_raw, "dt_raw"); _contig(a_log, "a_log"); _contig(state, "state")
+    out = torch.empty((T, E), dtype=xc.dtype, device=xc.device)
+    chunks = _chunks_for(int(lib.rllm_scan_chunk()), max_q_len, num_seqs)
+    work = torch.empty(num_seqs * chunks * (N + 1) * E, dtype=torch.float32, device=xc.device) if chunks else None
+    work_dt = work[num_seqs * chunks * N * E:] if chunks else None
+    _check(lib.rllm_selective_scan(_ptr(xc), _ptr(dt_raw), _ptr(dt_bias), _ptr(bc), c_int(bc.stride(0)), c_int(b_off),
+                                   c_int(c_off), _ptr(a_log), _ptr(dskip), _ptr(z), c_int(z.stride(0)),
+                                   c_int(dtype_code(xc.dtype)), c_int(dtype_code(a_log.dtype)), _ptr(state),
+                                   _ptr(work), _ptr(work_dt), _ptr(q_start), _ptr(slots), c_int(state.shape[0]),
+                                   c_int(num_seqs), c_int(chunks), _ptr(out), c_int(E), c_int(N), _ptr(err),
+                                   _stream()), "selective_scan")
+    return out

@@ -33,8 +33,8 @@ class CacheLayout:
     the run's mixer keeps nothing)."""
 
     groups: List[object]
-    owners: List[List[int]]
-    run_group: List[Optional[int]]
+    owners: List[list]
+    run_group: List[object]
     run_owner: List[Optional[int]]
 
 
@@ -101,33 +101,48 @@ class DecoderModel:
     # -- cache ------------------------------------------------------------
     def _cache_layout(self) -> CacheLayout:
         groups: List[object] = []
-        owners: List[List[int]] = []
-        run_group: List[Optional[int]] = []
+        owners: List[list] = []
+        run_group: List[object] = []
         run_owner: List[Optional[int]] = []
-        for i, run in enumerate(self.spec.order):
+
+        def needs_of(run) -> Tuple[Tuple[object, ...], bool]:
             need = self.blocks[run.layer].mixer.cache_need()
             if need is None:
+                return (), False
+            return (tuple(need), True) if isinstance(need, (tuple, list)) else ((need,), False)
+
+        for i, run in enumerate(self.spec.order):
+            needs, several = needs_of(run)
+            if not needs:
                 run_group.append(None)
                 run_owner.append(None)
                 continue
             # a slot keeps what its owner and every run that reads it need: the same rows, the widest window
+            needs = list(needs)
             for j, other in enumerate(self.spec.order):
                 if other.cache != run.cache or j == i:
                     continue
-                theirs = self.blocks[other.layer].mixer.cache_need()
-                wide = need.widened(theirs) if hasattr(need, "widened") and type(theirs) is type(need) else \
-                    (need if theirs == need else None)
-                if wide is None:
+                theirs, _ = needs_of(other)
+                if len(theirs) != len(needs):
                     raise ValueError(f"order[{i}] and order[{j}] use cache slot {run.cache} but keep "
-                                     f"{need} and {theirs}")
-                need = wide
-            if need not in groups:
-                groups.append(need)
-                owners.append([])
-            g = groups.index(need)
-            if run.cache == i:
-                owners[g].append(i)
-            run_group.append(g)
+                                     f"{needs} and {list(theirs)}")
+                for k, (mine, other_need) in enumerate(zip(needs, theirs)):
+                    wide = mine.widened(other_need) if hasattr(mine, "widened") and type(other_need) is type(mine) \
+                        else (mine if other_need == mine else None)
+                    if wide is None:
+                        raise ValueError(f"order[{i}] and order[{j}] use cache slot {run.cache} but keep "
+                                         f"{mine} and {other_need}")
+                    needs[k] = wide
+            gs = []
+            for k, need in enumerate(needs):
+                if need not in groups:
+                    groups.append(need)
+                    owners.append([])
+                g = groups.index(need)
+                if run.cache == i:
+                    owners[g].append((i, k) if several else i)
+                gs.append(g)
+            run_group.append(tuple(gs) if several else gs[0])
             run_owner.append(run.cache)
         return CacheLayout(groups, owners, run_group, run_owner)
 
@@ -143,13 +158,22 @@ class DecoderModel:
                                device=token_ids.device)
             ctx.extras["depth_history"] = hist
             h = self.embedding.forward(token_ids, ctx.err, out=hist[0])
+        elif self.spec.streams > 1:
+            # several copies of the residual, all equal to the embedding's output at the start
+            h = torch.empty((self.spec.streams, token_ids.numel(), self.spec.hidden_size), dtype=torch.float32,
+                            device=token_ids.device)
+            self.embedding.forward(token_ids, ctx.err, out=h)
         else:
             h = self.embedding.forward(token_ids, ctx.err)
         pending = None
         order = self.spec.order
         for i, run in enumerate(order):
             block = self.blocks[run.layer]
-            if getattr(block, "takes_next_norm", False) and i + 1 < len(order):
+            if getattr(block, "takes_next_block", False):
+                # the block that reads the streams next: this one may prepare its input in its last kernel
+                nxt = self.blocks[order[i + 1].layer] if i + 1 < len(order) else None
+                h, pending = block.forward(h, pending, ctx, storage.view(i), next_block=nxt)
+            elif getattr(block, "takes_next_norm", False) and i + 1 < len(order):
                 # the norm that reads the stream after this block: the block may prepare its input
                 nxt = getattr(self.blocks[order[i + 1].layer], "norms", None)
                 h, pending = block.forward(h, pending, ctx, storage.view(i), next_norm=nxt[0] if nxt else None)
@@ -159,7 +183,15 @@ class DecoderModel:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=h.device)
         if not isinstance(pending, torch.Tensor):
             pending = None                      # a block that adds into the stream itself left it complete
-        xn = self.final_norm.gather_forward(h, pending, logit_rows, ctx.act_dtype)
+        if h.dim() == 3:
+            # the output reads the sum of the streams; a norm without statistics joins that kernel
+            from ..kernels import ops
+            fused = self.final_norm.elementwise() if hasattr(self.final_norm, "elementwise") else None
+            xn = ops.streams_read(h, None, fused, ctx.act_dtype, rows=logit_rows)
+            if fused is None:
+                xn = self.final_norm.forward(xn, ctx.act_dtype)
+        else:
+            xn = self.final_norm.gather_forward(h, pending, logit_rows, ctx.act_dtype)
         return self.head.forward(xn)
 
 

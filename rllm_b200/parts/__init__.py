@@ -1,7 +1,7 @@
 """Parts a layer is put together from.  Importing the package registers the
 built-in kinds."""
-from . import (attention, block, gated_block, latent_attention, mingru, mlp, norm, rotary,  # noqa: F401  (registration)
-               routed_experts)
+from . import (attention, block, gated_block, hyper_block, latent_attention, lightning, mingru, mlp, norm,  # noqa: F401  (registration)
+               parallel, rotary, routed_experts, selective_scan)
 from .base import (FeedForward, KVCacheView, Mixer, Norm, Part, PositionEncoding, StateCacheView,
                    StepContext)
 from .registry import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, build_part,

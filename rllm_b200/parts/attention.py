@@ -13,11 +13,21 @@ Portions of prompts and single decoded tokens are one code path: the tokens
 of this step are written to the cache first and every query then reads keys
 0 .. its own position (or its window) from the cache.
 
+Two options beyond the Llama's: ``v_dim``, a value head of another size than
+a query and key head (the output projection then reads num_heads * v_dim), and
+``qk_norm`` = eps: every query head and every key head is divided by its root
+mean square (eps inside the root) and multiplied by a weight [head_dim] that
+all heads share (tensor names "q_norm", "k_norm").  With either, the tokens'
+keys (normalised) and values are written to the pages by one kernel and the
+attention reads everything from there; these two take no rotation.
+
 params: hidden_size, num_heads, num_kv_heads, head_dim, window (None: all
 keys), scale (None: 1/sqrt(head_dim)), position (PartSpec), shares_kv (True:
 the run reads another run's cache, has no k/v projections and writes nothing),
+v_dim (None: head_dim), qk_norm (None, or eps),
 tensor_names (the names of the four projection weights below the part's prefix,
-keys "q", "k", "v", "o": the architecture gives them, the part knows none).
+keys "q", "k", "v", "o", with qk_norm also "q_norm", "k_norm": the architecture
+gives them, the part knows none).
 """
 from __future__ import annotations
 
@@ -50,19 +60,28 @@ class PagedAttention(Mixer):
         self.window = p.get("window")
         self.scale = float(p["scale"]) if p.get("scale") is not None else 1.0 / math.sqrt(self.d)
         self.shares_kv = bool(p.get("shares_kv", False))
+        self.dv = int(p.get("v_dim") or self.d)
+        self.qk_eps = float(p["qk_norm"]) if p.get("qk_norm") is not None else None
+        self.plain = self.dv == self.d and self.qk_eps is None      # the Llama's form: rotation fused with the write
         if self.nq % self.nkv:
             raise ValueError(f"num_heads {self.nq} must be a multiple of num_kv_heads {self.nkv}")
-        if self.d % 16 or self.d > 256:
+        if self.plain and (self.d % 16 or self.d > 256):
             raise ValueError(f"head_dim {self.d}: the attention kernels take multiples of 16 up to 256")
+        if self.dv > 256:
+            raise ValueError(f"v_dim {self.dv}: the attention kernels take value heads up to 256")
         names = dict(p.get("tensor_names") or ())
-        if sorted(names) != ["k", "o", "q", "v"]:
-            raise ValueError("an attention spec names its weights: tensor_names with the keys q, k, v, o")
+        want = ["k", "o", "q", "v"] + (["k_norm", "q_norm"] if self.qk_eps is not None else [])
+        if sorted(names) != sorted(want):
+            raise ValueError(f"an attention spec names its weights: tensor_names with the keys {sorted(want)}")
         self.names = {k: str(v) for k, v in names.items()}
         pos = p.get("position")
         self.position = build_part("position_encoding", pos if pos is not None else PartSpec.of("none"),
                                    prefix=prefix)
         if getattr(self.position, "interleaved", False):
             raise ValueError("this mixer's kernels rotate halves; an interleaved rotation is not among them")
+        if not self.plain and pos is not None and pos.kind != "none":
+            raise ValueError("attention with v_dim or qk_norm takes no position encoding")
+        self.w_qn = self.w_kn = None
         self.w_qkv: Optional[torch.Tensor] = None
         self.w_o: Optional[torch.Tensor] = None
 
@@ -79,8 +98,14 @@ class PagedAttention(Mixer):
         specs = [TensorSpec(q, (self.nq * self.d, self.hidden))]
         if not self.shares_kv:
             specs += [TensorSpec(k, (self.nkv * self.d, self.hidden)),
-                      TensorSpec(v, (self.nkv * self.d, self.hidden))]
-        specs.append(TensorSpec(o, (self.hidden, self.nq * self.d)))
+                      TensorSpec(v, (self.nkv * self.dv, self.hidden))]
+        specs.append(TensorSpec(o, (self.hidden, self.nq * self.dv)))
+        if self.qk_eps is not None:
+            specs.append(TensorSpec(self.prefix + self.names["q_norm"], (self.d,), role="vector",
+                                    init=("one_plus_normal", 0.1)))
+            if not self.shares_kv:
+                specs.append(TensorSpec(self.prefix + self.names["k_norm"], (self.d,), role="vector",
+                                        init=("one_plus_normal", 0.1)))
         return specs
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
@@ -91,13 +116,50 @@ class PagedAttention(Mixer):
             # stacked [Wq; Wk; Wv]: one matrix product gives a token's q, k and v side by side
             self.w_qkv = torch.cat([tensors[q], tensors[k], tensors[v]], dim=0).contiguous()
         self.w_o = tensors[o]
+        if self.qk_eps is not None:
+            self.w_qn = tensors[self.prefix + self.names["q_norm"]].contiguous()
+            self.w_kn = self.w_qn if self.shares_kv else \
+                tensors[self.prefix + self.names["k_norm"]].to(self.w_qn.dtype).contiguous()
 
     def cache_need(self):
-        return KVPagesNeed(self.nkv, self.d, self.window)
+        return KVPagesNeed(self.nkv, self.d, self.window, v_dim=None if self.dv == self.d else self.dv)
 
     # -- compute ----------------------------------------------------------
     def fused_residual(self, num_rows: int, dtype: torch.dtype) -> bool:
-        return fused_residual_takes(num_rows, dtype, self.w_qkv, self.w_o)
+        return self.plain and fused_residual_takes(num_rows, dtype, self.w_qkv, self.w_o)
+
+    def _attend_from_pages(self, qkv: torch.Tensor, ctx: StepContext, cache: KVCacheView) -> torch.Tensor:
+        """Heads with norms or values of their own size: one kernel normalises the queries in place and writes
+        the (normalised) keys and the values into the pages; the attention then reads every key, the tokens'
+        own included, from the pages.  Where keys and values have one size, the tensor-core kernels take it
+        from there; else the CUDA-core kernel, which takes any two sizes."""
+        T = qkv.shape[0]
+        table = ctx.block_tables[cache.group]
+        writes = cache.writes and not self.shares_kv
+        ops.head_norm_kv_write(qkv, ctx.positions, ctx.token_seq, self.w_qn, self.w_kn, self.qk_eps or 0.0, table,
+                               cache.k, cache.v, self.nq, 0 if self.shares_kv else self.nkv, self.d, self.dv,
+                               ctx.err, write_kv=writes)
+        out = torch.empty((T, self.nq * self.dv), dtype=qkv.dtype, device=qkv.device)
+        window, stride = int(self.window or 0), qkv.shape[1]
+        if self.dv == self.d and self.d % 16 == 0 and ops.use_mma_attention(qkv.dtype, self.nq, self.nkv, self.d):
+            nd = ctx.num_decode
+            if nd:
+                ops.attention_decode_bf16(qkv, stride, out, cache.k, cache.v, table, ctx.seq_lens, nd,
+                                          max(ctx.seq_lens_host[:nd]), self.nq, self.nkv, self.d, window, self.scale,
+                                          ctx.err, write_kv=False)
+            if T > nd:
+                if ops.use_tcgen05_attention(qkv.dtype, self.nq, self.nkv, self.d, cache.k.shape[2]):
+                    ops.attention_prefill_tcgen05(qkv, stride, out, cache.k, cache.v, table, ctx.q_start,
+                                                  ctx.seq_lens, nd, ctx.num_seqs, T - nd, self.nq, self.nkv, self.d,
+                                                  window, self.scale, ctx.err)
+                else:
+                    ops.attention_prefill_bf16(qkv, stride, out, cache.k, cache.v, table, ctx.q_start, ctx.seq_lens,
+                                               nd, ctx.num_seqs, T - nd, self.nq, self.nkv, self.d, window,
+                                               self.scale, ctx.err)
+            return out
+        ops.attention_simt_kv(qkv, stride, out, cache.k, cache.v, table, ctx.positions, ctx.token_seq, self.nq,
+                              self.nkv, window, self.scale, ctx.err)
+        return out
 
     def forward(self, x, ctx: StepContext, cache: KVCacheView, residual=None):
         out = self.attend(linear(x, self.w_qkv), ctx, cache)          # qkv [T, (nq + 2 nkv) d]
@@ -106,6 +168,8 @@ class PagedAttention(Mixer):
     def attend(self, qkv: torch.Tensor, ctx: StepContext, cache: KVCacheView) -> torch.Tensor:
         """From the tokens' projections (q, k and v heads side by side) to the attention's output
         [T, nq * d], before the output projection: position encoding, cache write, attention."""
+        if not self.plain:
+            return self._attend_from_pages(qkv, ctx, cache)
         x = qkv
         T = qkv.shape[0]
         nkv_here = 0 if self.shares_kv else self.nkv

@@ -14,7 +14,8 @@ Norm            forward(x_f32[T,H]) -> act[T,H]
 PositionEncoding  apply(q[T,nq,d], k[T,nkv,d], positions) in place; optionally
                 fused_rotary(device) -> (inv_freq float64[rd/2], rd) so that a mixer can
                 fuse the rotation into its cache write
-Mixer           cache_need() -> KVPagesNeed | StateNeed | None
+Mixer           cache_need() -> KVPagesNeed | StateNeed | None, or a tuple of needs (pages and a
+                state, two states); forward then gets a tuple of views in that order
                 forward(x act[T,H], ctx StepContext, cache view) -> act[T,H]
 FeedForward     forward(x act[T,H]) -> act[T,H]
 Block           forward(h_f32[T,H], pending act[T,H]|None, ctx, cache) -> (h_f32, pending)
@@ -102,6 +103,16 @@ class NormedRows:
     x: torch.Tensor
     by: torch.Tensor
     eps: float
+
+
+@dataclass
+class PreparedInput:
+    """The stream is complete, and ``x`` [T, H] is already the first sublayer's input of the block ``key``
+    (that block's own read of the stream and its first norm, in the activation dtype), prepared by the
+    block ahead in its last kernel; any other reader ignores it."""
+
+    x: torch.Tensor
+    key: object
 
 
 @dataclass

@@ -1,7 +1,7 @@
 """Token embedding and output head.
 
-Embedding: a row gather without scaling (crates/rllm-model/src/llama.rs:329-337)
-that writes the float32 residual stream.  Head: logits = x . W_out^T without
+Embedding: a row gather (crates/rllm-model/src/llama.rs:329-337; without scaling
+there, with an optional constant factor here) that writes the float32 residual stream.  Head: logits = x . W_out^T without
 bias (llama.rs:57-59, 70), W_out = ``lm_head.weight`` if the file has it, else
 the embedding table (llama.rs:174-180); the logits are float32, straight from
 the accumulator.  The head runs on the rows that were asked for only.
@@ -19,13 +19,14 @@ from .spec import PartSpec, TensorSpec
 
 
 class TokenEmbedding(Part):
-    """params: vocab_size, hidden_size, name."""
+    """params: vocab_size, hidden_size, name, scale (optional: the rows are multiplied by it)."""
 
     def __init__(self, spec: PartSpec, prefix: str = ""):
         super().__init__(spec, prefix)
         self.vocab = int(spec["vocab_size"])
         self.hidden = int(spec["hidden_size"])
         self.name = str(spec["name"])
+        self.scale = float(spec.get().get("scale") or 1.0)
         self.weight: Optional[torch.Tensor] = None
 
     def tensor_specs(self) -> List[TensorSpec]:
@@ -37,7 +38,7 @@ class TokenEmbedding(Part):
     def forward(self, token_ids: torch.Tensor, err: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         if out is None:
             out = torch.empty((token_ids.numel(), self.hidden), dtype=torch.float32, device=token_ids.device)
-        ops.embedding(token_ids, self.weight, out, err)
+        ops.embedding(token_ids, self.weight, out, err, scale=self.scale)      # out [C, T, H]: C equal copies
         return out
 
 

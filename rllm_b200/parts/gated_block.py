@@ -129,7 +129,7 @@ class SandwichGatedBlock(Part):
                                    depth=depth if last else None)
         normed = b if last else None
         if not last:
-            if hasattr(self.ffn, "forward_slots"):
+            if hasattr(self.ffn, "forward_slots") and getattr(self.ffn, "shared", None) is None:
                 f, slot_w = self.ffn.forward_slots(b)
             else:
                 f, slot_w = self.ffn.forward(b), None

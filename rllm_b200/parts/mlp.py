@@ -3,8 +3,13 @@
 over the stacked weights [Wgate; Wup]; silu(z) = z / (1 + exp(-z)) and the
 product with up are computed in float32.
 
-params: hidden_size, intermediate_size, tensor_names (the names of the three
-weights below the part's prefix, keys "gate", "up", "down").
+``activation`` "gelu_tanh" puts 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
+in the place of the SiLU (one product over the stacked weights, then one kernel
+for the activation and the product with up).
+
+params: hidden_size, intermediate_size, activation ("silu" if absent),
+tensor_names (the names of the three weights below the part's prefix, keys
+"gate", "up", "down").
 """
 from __future__ import annotations
 
@@ -28,6 +33,9 @@ class GatedMLP(FeedForward):
         super().__init__(spec, prefix)
         self.hidden = int(spec["hidden_size"])
         self.inter = int(spec["intermediate_size"])
+        self.activation = str(spec.get().get("activation") or "silu")
+        if self.activation not in ops.ACTIVATIONS:
+            raise ValueError(f"activation {self.activation!r}; known: {sorted(ops.ACTIVATIONS)}")
         names = dict(spec.get().get("tensor_names") or ())
         if sorted(names) != ["down", "gate", "up"]:
             raise ValueError("a gated_mlp spec names its weights: tensor_names with the keys gate, up, down")
@@ -50,11 +58,13 @@ class GatedMLP(FeedForward):
         self.w_down = tensors[d]
 
     def fused_residual(self, num_rows: int, dtype: torch.dtype) -> bool:
-        return fused_residual_takes(num_rows, dtype, self.w_gate_up, self.w_down)
+        return self.activation == "silu" and fused_residual_takes(num_rows, dtype, self.w_gate_up, self.w_down)
 
     def forward(self, x, residual=None):
         act = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)
-        if isinstance(x, ScaledRows):
+        if self.activation != "silu":
+            ops.act_mul(linear(x, self.w_gate_up), act, self.activation)
+        elif isinstance(x, ScaledRows):
             # the rows' 1 / rms is applied to gate and up before the SiLU
             ops.gemm_small_m_rstd(x.x, x.parts, x.eps, self.w_gate_up, act, "silu_mul")
         elif ops.small_m_takes(x, self.w_gate_up):

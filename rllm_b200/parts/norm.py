@@ -56,3 +56,51 @@ class RMSNorm(Norm):
         out = torch.empty((rows.numel(), x.shape[1]), dtype=act_dtype, device=x.device)
         ops.rmsnorm(x, self.weight, self.eps, out, delta=delta, rows=rows)
         return out
+
+
+@register_part("norm", "dynamic_tanh")
+class DynamicTanh(Norm):
+    """y = tanh(alpha * x) * w + c: a norm without statistics (no mean, no variance, no eps), element by
+    element in float32.  alpha is one learned number, w and c vectors.
+
+    params: size, name, alpha_name, shift_name (tensor names below the prefix)."""
+    graph_safe = True
+
+    def __init__(self, spec: PartSpec, prefix: str = ""):
+        super().__init__(spec, prefix)
+        self.size = int(spec["size"])
+        self.name = prefix + str(spec["name"])
+        self.alpha_name = prefix + str(spec["alpha_name"])
+        self.shift_name = prefix + str(spec["shift_name"])
+        self.weight: Optional[torch.Tensor] = None
+        self.shift: Optional[torch.Tensor] = None
+        self.alpha: Optional[torch.Tensor] = None
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        return [TensorSpec(self.name, (self.size,), role="vector", init=("one_plus_normal", 0.1)),
+                TensorSpec(self.shift_name, (self.size,), role="vector", init=("normal", 0.1)),
+                TensorSpec(self.alpha_name, (), role="vector", init=("one_plus_normal", 0.1))]
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.weight = tensors[self.name].contiguous()
+        self.shift = tensors[self.shift_name].to(self.weight.dtype).contiguous()
+        self.alpha = tensors[self.alpha_name].float().reshape(1).contiguous()
+
+    def elementwise(self):
+        """(alpha float32 [1], weight, shift): what a kernel needs to apply this norm to a value it holds."""
+        return self.alpha, self.weight, self.shift
+
+    def forward(self, x: torch.Tensor, act_dtype: torch.dtype) -> torch.Tensor:
+        out = torch.empty(x.shape, dtype=act_dtype, device=x.device)
+        ops.dyt(x, self.alpha, self.weight, self.shift, out)
+        return out
+
+    def add_forward(self, x: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
+        out = torch.empty(x.shape, dtype=delta.dtype, device=x.device)
+        ops.dyt(x, self.alpha, self.weight, self.shift, out, delta=delta, writeback=True)
+        return out
+
+    def gather_forward(self, x, delta, rows, act_dtype):
+        out = torch.empty((rows.numel(), x.shape[1]), dtype=act_dtype, device=x.device)
+        ops.dyt(x, self.alpha, self.weight, self.shift, out, delta=delta, rows=rows)
+        return out

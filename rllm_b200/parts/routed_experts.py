@@ -14,9 +14,18 @@ read back to the host.  ``forward_slots`` returns the pairs' results [T * top, H
 and the weights [T, top] for a reader that takes the weighted sum itself;
 ``forward`` takes it.
 
-params: hidden_size, inner_size, num_experts, top, limit, alpha, up_shift,
+``score`` "sigmoid": the experts' scores do not compete, s = sigmoid(z); the ``top``
+largest of s + c are chosen, c a stored vector [experts] that only the choice sees
+(tensor name "correction", optional); the weights are s * ``route_scale``.
+
+``shared``: the ``PartSpec`` of a feed-forward that every token runs beside its experts;
+its result is added, multiplied by sigmoid(w . x) with one stored row w [1, hidden]
+(tensor name "shared_gate") if that name is given.
+
+params: hidden_size, inner_size, num_experts, top, limit, alpha, up_shift, score
+("softmax" if absent), route_scale (1), shared (None),
 tensor_names (keys "router", "gate", "up", "down"; the last three with ``{e}`` where
-the expert's number stands).
+the expert's number stands; optional "correction", "shared_gate").
 """
 from __future__ import annotations
 
@@ -27,7 +36,7 @@ import torch
 from ..kernels import ops
 from .base import FeedForward
 from .linear import linear
-from .registry import register_part
+from .registry import build_part, register_part
 from .spec import PartSpec, TensorSpec
 
 
@@ -45,13 +54,23 @@ class RoutedExperts(FeedForward):
         self.limit = float(p["limit"]) if p.get("limit") is not None else float("inf")
         self.alpha = float(p.get("alpha", 1.0))
         self.up_shift = float(p.get("up_shift", 0.0))
-        if self.up_shift != 1.0:
-            raise ValueError("the expert kernel computes (u' + 1); another up_shift is not built")
+        self.score = str(p.get("score") or "softmax")
+        if self.score not in ("softmax", "sigmoid"):
+            raise ValueError(f"score {self.score!r}; known: softmax, sigmoid")
+        self.route_scale = float(p.get("route_scale") if p.get("route_scale") is not None else 1.0)
         names = dict(p.get("tensor_names") or ())
-        if sorted(names) != ["down", "gate", "router", "up"]:
-            raise ValueError("a routed_experts spec names its tensors: tensor_names with the keys router, gate, up, down")
+        if not {"down", "gate", "router", "up"} <= set(names) or \
+                set(names) - {"down", "gate", "router", "up", "correction", "shared_gate"}:
+            raise ValueError("a routed_experts spec names its tensors: tensor_names with the keys router, gate, up, "
+                             "down (and optionally correction, shared_gate)")
+        if self.score == "softmax" and ("correction" in names or self.route_scale != 1.0):
+            raise ValueError("a correction of the choice and a scale of the weights go with score 'sigmoid'")
         self.names = {k: prefix + str(v) for k, v in names.items()}
-        self.w_router = self.w_gate_up = self.w_down = None
+        self.shared = build_part("feed_forward", p["shared"], prefix=prefix + str(p["shared"].get().get("tensor_prefix") or "")) \
+            if p.get("shared") is not None else None
+        if "shared_gate" in names and self.shared is None:
+            raise ValueError("shared_gate without a shared feed-forward")
+        self.w_router = self.w_gate_up = self.w_down = self.correction = self.w_shared_gate = None
 
     def _expert(self, key: str, e: int) -> str:
         return self.names[key].format(e=e)
@@ -62,6 +81,12 @@ class RoutedExperts(FeedForward):
             specs += [TensorSpec(self._expert("gate", e), (self.inner, self.hidden), init=("normal", 0.1)),
                       TensorSpec(self._expert("up", e), (self.inner, self.hidden), init=("normal", 0.1)),
                       TensorSpec(self._expert("down", e), (self.hidden, self.inner), init=("normal", 0.1))]
+        if "correction" in self.names:
+            specs.append(TensorSpec(self.names["correction"], (self.experts,), role="vector", init=("normal", 0.2)))
+        if self.shared is not None:
+            specs += self.shared.tensor_specs()
+        if "shared_gate" in self.names:
+            specs.append(TensorSpec(self.names["shared_gate"], (1, self.hidden), init=("normal", 0.1)))
         return specs
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
@@ -70,16 +95,32 @@ class RoutedExperts(FeedForward):
         self.w_gate_up = torch.stack([torch.cat([tensors[self._expert("gate", e)], tensors[self._expert("up", e)]], dim=0)
                                       for e in range(self.experts)]).contiguous()
         self.w_down = torch.stack([tensors[self._expert("down", e)] for e in range(self.experts)]).contiguous()
+        if "correction" in self.names:
+            self.correction = tensors[self.names["correction"]].float().contiguous()
+        if self.shared is not None:
+            self.shared.load(tensors)
+        if "shared_gate" in self.names:
+            self.w_shared_gate = tensors[self.names["shared_gate"]]
 
     def forward_slots(self, x: torch.Tensor):
         # the logits are one matrix product with a float32 result (float32 accumulation from the first term
         # on), softmax and choice a small kernel (``ops.moe_route`` is the same in one kernel, a warp a token:
         # the form the two are checked against)
-        ids, scores = ops.moe_choose(linear(x, self.w_router, out_dtype=torch.float32), self.top)
-        return ops.moe_experts(x, ids, self.w_gate_up, self.w_down, self.limit, self.alpha), scores
+        logits = linear(x, self.w_router, out_dtype=torch.float32)
+        if self.score == "sigmoid":
+            ids, scores = ops.moe_choose_sigmoid(logits, self.top, self.correction, self.route_scale)
+        else:
+            ids, scores = ops.moe_choose(logits, self.top)
+        return ops.moe_experts(x, ids, self.w_gate_up, self.w_down, self.limit, self.alpha, self.up_shift), scores
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         y, scores = self.forward_slots(x)
         out = torch.empty_like(x)
-        ops.weighted_slot_sum(y, scores, out)
+        if self.shared is None:
+            ops.weighted_slot_sum(y, scores, out)
+            return out
+        gate = None
+        if self.w_shared_gate is not None:
+            gate = linear(x, self.w_shared_gate, out_dtype=torch.float32).reshape(-1)
+        ops.weighted_slot_sum(y, scores, out, extra=self.shared.forward(x), extra_gate=gate)
         return out

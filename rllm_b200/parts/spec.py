@@ -98,6 +98,7 @@ class ModelSpec:
     head: PartSpec
     max_positions: int
     eos_token_ids: Tuple[int, ...] = ()
+    streams: int = 1                 # parallel copies of the residual (blocks that read and write them all)
 
     def validate(self) -> None:
         for i, run in enumerate(self.order):
@@ -118,19 +119,26 @@ class KVPagesNeed:
     """Keys and values of every token (``window`` None) or of the last
     ``window`` tokens, in pages.  ``values`` False: a token keeps ONE row of
     ``head_dim`` values per kv head that serves as key and as value (a latent);
-    the storage then has no second buffer."""
+    the storage then has no second buffer.  ``v_dim``: the size of a value row
+    where it is not a key row's (None: ``head_dim``)."""
 
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     values: bool = True
+    v_dim: Optional[int] = None
+
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.v_dim is None else self.v_dim
 
     def widened(self, other: "KVPagesNeed") -> Optional["KVPagesNeed"]:
         """The need that keeps what both keep, if the rows are the same and only the windows differ."""
-        if (self.num_kv_heads, self.head_dim, self.values) != (other.num_kv_heads, other.head_dim, other.values):
+        if (self.num_kv_heads, self.head_dim, self.values, self.value_dim) != \
+                (other.num_kv_heads, other.head_dim, other.values, other.value_dim):
             return None
         w = None if self.window is None or other.window is None else max(self.window, other.window)
-        return KVPagesNeed(self.num_kv_heads, self.head_dim, w, self.values)
+        return KVPagesNeed(self.num_kv_heads, self.head_dim, w, self.values, self.v_dim)
 
 
 @dataclass(frozen=True)
