@@ -158,7 +158,7 @@ class DecoderModel:
                                device=token_ids.device)
             ctx.extras["depth_history"] = hist
             h = self.embedding.forward(token_ids, ctx.err, out=hist[0])
-        elif self.spec.streams > 1:
+        elif self.spec.streams > 0:
             # several copies of the residual, all equal to the embedding's output at the start
             h = torch.empty((self.spec.streams, token_ids.numel(), self.spec.hidden_size), dtype=torch.float32,
                             device=token_ids.device)

@@ -98,7 +98,8 @@ class ModelSpec:
     head: PartSpec
     max_positions: int
     eos_token_ids: Tuple[int, ...] = ()
-    streams: int = 1                 # parallel copies of the residual (blocks that read and write them all)
+    streams: int = 0                 # > 0: the residual is that many parallel streams [S, T, H] (blocks that read
+                                     # and write them all); 0: the one residual [T, H]
 
     def validate(self) -> None:
         for i, run in enumerate(self.order):

@@ -203,3 +203,15 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens, layers_out: Optional[
         if layers_out is not None:
             layers_out.append(xs.sum(dim=0))
     return tanh_norm(w, "final.norm", xs.sum(dim=0)) @ w["embed"].t()
+
+
+logits = forward
+
+
+def greedy(cfg: dict, w: Dict[str, torch.Tensor], prompt: List[int], n_new: int) -> List[int]:
+    seq, out = list(prompt), []
+    for _ in range(n_new):
+        t = int(torch.argmax(forward(cfg, w, seq)[-1]))
+        out.append(t)
+        seq.append(t)
+    return out
