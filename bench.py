@@ -409,6 +409,23 @@ def fasulix(layers, width, heads, dim, rot, vdim, q_rank, kv_rank, gru, experts,
                        for i in range(layers)]}
 
 
+def fevolorn(layers, width, streams, lheads, ldim, lvdim, heads, kv_heads, dim, vdim, window, inner, state, dt_rank,
+             experts, top, ff, shared, dense, vocab):
+    """layers of the pattern [lightning + dense, parallel + experts, lightning + experts, parallel + experts]."""
+    moe = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top, "scale": 2.5},
+           "shared": {"ff": shared}}
+    lightning = {"heads": lheads, "dim": ldim, "vdim": lvdim,
+                 "decay": [1.0 - 2.0 ** (-5.0 - 3.0 * h / max(1, lheads - 1)) for h in range(lheads)]}
+    parallel = {"left": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": dim ** -0.5,
+                         "mask": {"size": window}},
+                "right": {"inner": inner, "state": state, "dt_rank": dt_rank, "conv": 4}}
+    kinds = ["lightning", "parallel", "lightning", "parallel"]
+    return {"architecture": "Fevolorn", "vocab": vocab, "width": width, "streams": streams, "norm": {"eps": 1e-6},
+            "embedding": {"scale": 1.0}, "max_positions": 8192,
+            "layers": [{"type": kinds[i % 4], "mixer": lightning if kinds[i % 4] == "lightning" else parallel,
+                        "mlp": {"kind": "dense", "ff": dense} if i % 4 == 0 else moe} for i in range(layers)]}
+
+
 # (name, Fasulix sizes, the Llama beside it: same width, layers, heads and vocabulary, head size dim + rot,
 #  an intermediate size of top * ff, so that a token multiplies as many feed-forward weights)
 DESIGN_SIZES = [
@@ -419,6 +436,19 @@ DESIGN_SIZES = [
                    experts=32, top=4, ff=1024, window=1024, vocab=32768),
      dict(layers=4, hidden=2048, heads=16, kv_heads=4, head_dim=128, inter=4096)),
 ]
+
+
+# Fevolorn beside Fasulix (the closest design: recurrences, windowed attention and routed experts in one stack) of
+# equal width, layers, vocabulary, experts and expert width, and the Llama of that width.  w1024 keeps the
+# design's own head shape (values twice as wide as keys), w2048 has keys and values of one size.
+FEVOLORN_SIZES = {
+    "w1024": dict(layers=4, width=1024, streams=4, lheads=8, ldim=64, lvdim=128, heads=16, kv_heads=4, dim=64,
+                  vdim=128, window=512, inner=2048, state=16, dt_rank=64, experts=16, top=2, ff=1024, shared=1024,
+                  dense=2048, vocab=32768),
+    "w2048": dict(layers=4, width=2048, streams=4, lheads=16, ldim=128, lvdim=128, heads=16, kv_heads=4, dim=128,
+                  vdim=128, window=1024, inner=4096, state=16, dt_rank=128, experts=32, top=4, ff=1024, shared=2048,
+                  dense=4096, vocab=32768),
+}
 
 
 def compare_designs(args):
@@ -464,6 +494,26 @@ def compare_designs(args):
             return 2.0 * M * heads * Kd * N, 2.0 * (a[0].numel() + a[1].numel() + M * heads * N)
         if name == "mingru_scan":
             return 0.0, 2.0 * (a[0].numel() + a[7].numel())
+        if name == "lightning_scan":
+            heads, d, dv = a[4].shape[1:]
+            return 0.0, a[0].shape[0] * heads * (4.0 * d + 2.0 * dv + 4.0 * dv) + 8.0 * S * heads * d * dv
+        if name == "selective_scan":
+            return 0.0, a[0].numel() * 10.0 + 8.0 * S * a[9].shape[1] * a[9].shape[2]
+        if name == "causal_conv":
+            return 0.0, a[0].numel() * 4.0
+        if name == "streams_read":
+            return 0.0, a[0].numel() * 4.0 + a[0][0].numel() * 2.0
+        if name == "streams_write":
+            return 0.0, a[0].numel() * 8.0 + a[0][0].numel() * 4.0
+        if name in ("head_norm_kv_write", "act_mul"):
+            return 0.0, 4.0 * a[0].numel()
+        if name in ("rms_mean2", "gated_rmsnorm"):
+            return 0.0, 6.0 * a[0].numel()
+        if name == "attention_simt_kv":
+            dk, dv, nq, nkv, window = a[3].shape[3], a[4].shape[3], a[8], a[9], a[10]
+            vis = sum(min(p + 1, window or p + 1) for p in range(ctx - Tn // S, ctx)) * S
+            keys = S * min(ctx, (window or ctx) + Tn // S)
+            return 2.0 * (dk + dv) * nq * vis, 2.0 * (keys * nkv * (dk + dv) + Tn * nq * (dk + dv))
         if name == "gated_postnorm_add":
             return 0.0, 8.0 * a[0].numel() + 2.0 * (a[2].numel() + 2 * a[3].numel())
         if name == "depth_average":
@@ -486,7 +536,9 @@ def compare_designs(args):
             "latent_attention_mma", "attention_prefill_tcgen05", "attention_prefill_bf16", "attention_decode_bf16",
             "moe_experts", "moe_route", "head_gemm", "mingru_scan", "gated_postnorm_add", "depth_average", "rmsnorm",
             "silu_mul", "latent_prep", "latent_q_rot", "rope_kv_write", "gemm_small_m", "moe_choose", "gemm_small_m_residual",
-            "gemm_small_m_rstd", "gemm_tcgen05", "embedding")]
+            "gemm_small_m_rstd", "gemm_tcgen05", "embedding", "lightning_scan", "selective_scan", "causal_conv",
+            "streams_read", "streams_write", "head_norm_kv_write", "attention_simt_kv", "rms_mean2", "gated_rmsnorm",
+            "act_mul", "moe_choose_sigmoid", "weighted_slot_sum")]
         saved, log = {}, []
 
         def wrap(name, fn):
@@ -606,13 +658,16 @@ def compare_designs(args):
     for name, fx, ll in DESIGN_SIZES:
         if args.design_size and name != args.design_size:
             continue
-        f = measure("fasulix", fasulix(**fx))
+        row = {"size": name}
+        if args.design == "fevolorn":
+            row["fevolorn"] = measure("fevolorn", fevolorn(**FEVOLORN_SIZES[name]))
+        row["fasulix"] = measure("fasulix", fasulix(**fx))
         cfg = llama(ll["layers"], ll["hidden"], ll["heads"], ll["kv_heads"], ll["head_dim"], ll["inter"], 32.0, True)
         cfg["vocab_size"] = fx["vocab"]
-        m = measure("llama", cfg)
-        rows.append({"size": name, "fasulix": f, "llama": m})
+        row["llama"] = measure("llama", cfg)
+        rows.append(row)
     clocks.stop()
-    print(json.dumps({"metric": "fasulix_vs_llama_step_throughput", "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16",
+    print(json.dumps({"metric": "%s_vs_llama_step_throughput" % args.design, "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16",
                       "data": "synthetic", "prompt_len": T, "decode_batch": B, "decode_context": CTX,
                       "timing": "CUDA events; prefill: median of 5 steps after warm-up, 256 MiB written between steps; "
                                 "decode: %d graph steps on the device" % K,
@@ -635,7 +690,7 @@ def main():
     ap.add_argument("--no-standin", action="store_true", help="skip the library-operator stand-in")
     ap.add_argument("--settle-steps", type=int, default=SETTLE_STEPS,
                     help="untimed decode steps of a device-timed point before its warm-up steps (0 for a short capture under a profiler)")
-    ap.add_argument("--design", default=None, choices=["fasulix"],
+    ap.add_argument("--design", default=None, choices=["fasulix", "fevolorn"],
                     help="instead of the default workload: this design beside the Llama of equal size (prefill and "
                          "decode throughput, kernels against their rooflines)")
     ap.add_argument("--design-size", default=None, help="only this entry of the design comparison's sizes")

@@ -2,7 +2,12 @@
 //
 //   head_norm_kv_write   per-head RMS norm of queries (in place) and keys, and the write of
 //                        a token's keys and values into its cache pages; keys and values may
-//                        have different sizes per head; without norm weights it is the bare write
+//                        have different sizes per head; without norm weights it is the bare write.
+//                        The cache rows may be wider than the heads (dkp >= dk, dvp >= dv): the
+//                        rest of a row is written as zeros, and the queries then go, padded with
+//                        zeros to dkp a head, into a buffer of their own.  (Zeros change no score
+//                        and add columns of zeros to the result: keys and values of two sizes
+//                        can so be served by kernels that want one.)
 //   rms_mean             out = (1/n) sum_i rms(x_i) * w_i  over n = 2 inputs of one width
 //                        (branches of a mixer that run side by side)
 //   gated_rmsnorm        out = rms(x) * w * sigmoid(g)     (x float32, g in the activation dtype)
@@ -19,7 +24,8 @@ template <typename T, typename TW>
 __global__ void __launch_bounds__(32 * HN_WARPS)
 head_norm_kv_write_kernel(T* qkv, int stride, const int* positions, const int* token_seq, const TW* wq, const TW* wk,
                           float eps, const int* block_table, int max_blocks, T* kcache, T* vcache, int T_tokens, int nq,
-                          int nkv, int dk, int dv, int page_size, int num_pages, int write_kv, int* err) {
+                          int nkv, int dk, int dv, int dkp, int dvp, T* q_out, int page_size, int num_pages,
+                          int write_kv, int* err) {
   pdl_wait();
   pdl_launch();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -39,18 +45,20 @@ head_norm_kv_write_kernel(T* qkv, int stride, const int* positions, const int* t
       return;
     }
     const int kvh = (h - nq) % nkv;
-    dst = (h < nq + nkv) ? kcache + (((size_t)page * nkv + kvh) * page_size + pos % page_size) * dk
-                         : vcache + (((size_t)page * nkv + kvh) * page_size + pos % page_size) * dv;
+    dst = (h < nq + nkv) ? kcache + (((size_t)page * nkv + kvh) * page_size + pos % page_size) * dkp
+                         : vcache + (((size_t)page * nkv + kvh) * page_size + pos % page_size) * dvp;
+  } else if (q_out) {
+    dst = q_out + ((size_t)t * nq + h) * dkp;
   }
   if (h >= nq + nkv) {                                    // a value head: copied as it is
     const T* src = row + (size_t)nq * dk + (size_t)nkv * dk + (size_t)(h - nq - nkv) * dv;
-    for (int i = lane; i < dv; i += 32) dst[i] = src[i];
+    for (int i = lane; i < dvp; i += 32) dst[i] = (i < dv) ? src[i] : from_f32<T>(0.f);
     return;
   }
   T* src = row + (size_t)h * dk;                          // query heads, then key heads: both dk wide
   const TW* w = (h < nq) ? wq : wk;
   if (!w) {
-    if (dst) for (int i = lane; i < dk; i += 32) dst[i] = src[i];
+    if (dst) for (int i = lane; i < dkp; i += 32) dst[i] = (i < dk) ? src[i] : from_f32<T>(0.f);
     return;
   }
   float ss = 0.f;
@@ -58,23 +66,26 @@ head_norm_kv_write_kernel(T* qkv, int stride, const int* positions, const int* t
   ss = warp_sum(ss);
   const float r = 1.0f / sqrtf(ss / (float)dk + eps);
   T* o = dst ? dst : src;
-  for (int i = lane; i < dk; i += 32) o[i] = from_f32<T>(to_f32(src[i]) * r * to_f32(w[i]));
+  for (int i = lane; i < (dst ? dkp : dk); i += 32)
+    o[i] = (i < dk) ? from_f32<T>(to_f32(src[i]) * r * to_f32(w[i])) : from_f32<T>(0.f);
 }
 
 RLLM_EXPORT int rllm_head_norm_kv_write(void* qkv, int dtype, int stride, const int* positions, const int* token_seq,
                                         const void* wq, const void* wk, int w_dtype, float eps, const int* block_table,
                                         int max_blocks, void* kcache, void* vcache, int T, int nq, int nkv, int dk,
-                                        int dv, int page_size, int num_pages, int write_kv, int* err,
-                                        cudaStream_t stream) {
+                                        int dv, int dkp, int dvp, void* q_out, int page_size, int num_pages,
+                                        int write_kv, int* err, cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (nq <= 0 || nkv < 0 || dk <= 0 || dv <= 0) return RLLM_E_BADARG;
+  if (nq <= 0 || nkv < 0 || dk <= 0 || dv <= 0 || dkp < dk || dvp < dv) return RLLM_E_BADARG;
+  if (dkp > dk && !q_out) return RLLM_E_BADARG;          // padded keys want padded queries
   if (write_kv && (page_size <= 0 || num_pages <= 0 || max_blocks <= 0 || !kcache || !vcache)) return RLLM_E_BADARG;
   const long long warps = (long long)T * (nq + 2 * nkv);
   const unsigned blocks = (unsigned)((warps + HN_WARPS - 1) / HN_WARPS);
   RLLM_DISPATCH_DTYPE(dtype, TT, RLLM_DISPATCH_DTYPE(w_dtype, TW,
     (rllm_launch_pdl(head_norm_kv_write_kernel<TT, TW>, dim3(blocks), dim3(32 * HN_WARPS), (size_t)0, stream, (TT*)qkv,
                      stride, positions, token_seq, (const TW*)wq, (const TW*)wk, eps, block_table, max_blocks,
-                     (TT*)kcache, (TT*)vcache, T, nq, nkv, dk, dv, page_size, num_pages, write_kv, err))));
+                     (TT*)kcache, (TT*)vcache, T, nq, nkv, dk, dv, dkp, dvp, (TT*)q_out, page_size, num_pages,
+                     write_kv, err))));
   RLLM_LAUNCH_CHECK();
   return 0;
 }

@@ -1065,18 +1065,25 @@ def dyt(x: torch.Tensor, alpha: torch.Tensor, weight: torch.Tensor, shift: torch
 def head_norm_kv_write(qkv: torch.Tensor, positions: torch.Tensor, token_seq: torch.Tensor,
                        q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
                        block_table: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, nq: int, nkv: int,
-                       dk: int, dv: int, err: torch.Tensor, write_kv: bool = True) -> None:
+                       dk: int, dv: int, err: torch.Tensor, write_kv: bool = True,
+                       q_out: Optional[torch.Tensor] = None) -> None:
     """qkv [T, nq dk + nkv dk + nkv dv]: every query head (in place) and key head is divided by its root mean
     square and multiplied by the weight [dk] (None: left as it is); keys and values go to the token's place in
-    kcache [pages, nkv, page, dk] and vcache [pages, nkv, page, dv]."""
+    kcache [pages, nkv, page, dkp] and vcache [pages, nkv, page, dvp].  Cache rows wider than the heads (dkp > dk,
+    dvp > dv) are filled up with zeros; the queries then go to ``q_out`` [T, nq * dkp], filled up alike."""
     lib = build.load_library("mixer_glue")
     T = qkv.shape[0]
     assert qkv.shape[1] == nq * dk + nkv * (dk + dv) and qkv.stride(1) == 1
+    dkp = q_out.shape[1] // nq if q_out is not None else dk
+    dvp = dv
+    if q_out is not None:
+        assert q_out.shape == (T, nq * dkp) and q_out.dtype is qkv.dtype and q_out.is_contiguous()
     wd = q_weight.dtype if q_weight is not None else torch.float32
     if q_weight is not None:
         assert k_weight is not None and k_weight.dtype is wd and q_weight.numel() == dk and k_weight.numel() == dk
     if write_kv:
-        assert kcache.dtype is qkv.dtype and vcache.dtype is qkv.dtype and kcache.shape[3] == dk and vcache.shape[3] == dv
+        dvp = vcache.shape[3]
+        assert kcache.dtype is qkv.dtype and vcache.dtype is qkv.dtype and kcache.shape[3] == dkp and dvp >= dv
         _contig(kcache, "kcache"); _contig(vcache, "vcache"); _contig(block_table, "block_table")
         pages, page_size, max_blocks = kcache.shape[0], kcache.shape[2], block_table.shape[1]
     else:
@@ -1086,6 +1093,7 @@ def head_norm_kv_write(qkv: torch.Tensor, positions: torch.Tensor, token_seq: to
                                        c_float(eps), _ptr(block_table), c_int(max_blocks),
                                        _ptr(kcache if write_kv else None), _ptr(vcache if write_kv else None),
                                        c_int(T), c_int(nq), c_int(nkv if write_kv else 0), c_int(dk), c_int(dv),
+                                       c_int(dkp), c_int(dvp), _ptr(q_out),
                                        c_int(page_size), c_int(pages), c_int(1 if write_kv else 0), _ptr(err),
                                        _stream()), "head_norm_kv_write")
 

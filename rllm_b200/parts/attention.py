@@ -63,6 +63,14 @@ class PagedAttention(Mixer):
         self.dv = int(p.get("v_dim") or self.d)
         self.qk_eps = float(p["qk_norm"]) if p.get("qk_norm") is not None else None
         self.plain = self.dv == self.d and self.qk_eps is None      # the Llama's form: rotation fused with the write
+        # keys and values of two sizes: where the larger one is a size of the tensor-core kernels, the pages keep
+        # rows of that size for both (the rest zeros: no score changes, the result gains columns of zeros), and
+        # those kernels serve; twice the pages' bytes for the smaller of the two against CUDA-core attention
+        import os
+        self.dp = max(self.d, self.dv)
+        if self.d == self.dv or self.dp not in (16, 32, 64, 128) or self.nq // max(1, self.nkv) > 16 or \
+                os.environ.get("RLLM_ATTENTION_PAD") == "0":
+            self.dp = 0
         if self.nq % self.nkv:
             raise ValueError(f"num_heads {self.nq} must be a multiple of num_kv_heads {self.nkv}")
         if self.plain and (self.d % 16 or self.d > 256):
@@ -116,12 +124,19 @@ class PagedAttention(Mixer):
             # stacked [Wq; Wk; Wv]: one matrix product gives a token's q, k and v side by side
             self.w_qkv = torch.cat([tensors[q], tensors[k], tensors[v]], dim=0).contiguous()
         self.w_o = tensors[o]
+        if self.dp and self.dv < self.dp:
+            # the attention's result has dp columns a head, the last ones zeros: the projection skips them
+            w = self.w_o.new_zeros((self.hidden, self.nq, self.dp))
+            w[:, :, :self.dv] = self.w_o.view(self.hidden, self.nq, self.dv)
+            self.w_o = w.view(self.hidden, self.nq * self.dp).contiguous()
         if self.qk_eps is not None:
             self.w_qn = tensors[self.prefix + self.names["q_norm"]].contiguous()
             self.w_kn = self.w_qn if self.shares_kv else \
                 tensors[self.prefix + self.names["k_norm"]].to(self.w_qn.dtype).contiguous()
 
     def cache_need(self):
+        if self.dp:
+            return KVPagesNeed(self.nkv, self.dp, self.window)
         return KVPagesNeed(self.nkv, self.d, self.window, v_dim=None if self.dv == self.d else self.dv)
 
     # -- compute ----------------------------------------------------------
@@ -136,25 +151,29 @@ class PagedAttention(Mixer):
         T = qkv.shape[0]
         table = ctx.block_tables[cache.group]
         writes = cache.writes and not self.shares_kv
+        q_pad = torch.empty((T, self.nq * self.dp), dtype=qkv.dtype, device=qkv.device) if self.dp else None
         ops.head_norm_kv_write(qkv, ctx.positions, ctx.token_seq, self.w_qn, self.w_kn, self.qk_eps or 0.0, table,
                                cache.k, cache.v, self.nq, 0 if self.shares_kv else self.nkv, self.d, self.dv,
-                               ctx.err, write_kv=writes)
-        out = torch.empty((T, self.nq * self.dv), dtype=qkv.dtype, device=qkv.device)
+                               ctx.err, write_kv=writes, q_out=q_pad)
+        d, dv = (self.dp, self.dp) if self.dp else (self.d, self.dv)
+        if q_pad is not None:
+            qkv = q_pad
+        out = torch.empty((T, self.nq * dv), dtype=qkv.dtype, device=qkv.device)
         window, stride = int(self.window or 0), qkv.shape[1]
-        if self.dv == self.d and self.d % 16 == 0 and ops.use_mma_attention(qkv.dtype, self.nq, self.nkv, self.d):
+        if dv == d and d % 16 == 0 and ops.use_mma_attention(qkv.dtype, self.nq, self.nkv, d):
             nd = ctx.num_decode
             if nd:
                 ops.attention_decode_bf16(qkv, stride, out, cache.k, cache.v, table, ctx.seq_lens, nd,
-                                          max(ctx.seq_lens_host[:nd]), self.nq, self.nkv, self.d, window, self.scale,
+                                          max(ctx.seq_lens_host[:nd]), self.nq, self.nkv, d, window, self.scale,
                                           ctx.err, write_kv=False)
             if T > nd:
-                if ops.use_tcgen05_attention(qkv.dtype, self.nq, self.nkv, self.d, cache.k.shape[2]):
+                if ops.use_tcgen05_attention(qkv.dtype, self.nq, self.nkv, d, cache.k.shape[2]):
                     ops.attention_prefill_tcgen05(qkv, stride, out, cache.k, cache.v, table, ctx.q_start,
-                                                  ctx.seq_lens, nd, ctx.num_seqs, T - nd, self.nq, self.nkv, self.d,
+                                                  ctx.seq_lens, nd, ctx.num_seqs, T - nd, self.nq, self.nkv, d,
                                                   window, self.scale, ctx.err)
                 else:
                     ops.attention_prefill_bf16(qkv, stride, out, cache.k, cache.v, table, ctx.q_start, ctx.seq_lens,
-                                               nd, ctx.num_seqs, T - nd, self.nq, self.nkv, self.d, window,
+                                               nd, ctx.num_seqs, T - nd, self.nq, self.nkv, d, window,
                                                self.scale, ctx.err)
             return out
         ops.attention_simt_kv(qkv, stride, out, cache.k, cache.v, table, ctx.positions, ctx.token_seq, self.nq,

@@ -53,12 +53,16 @@ class TraceBuilder:
 
 
 def run_trace(model_dir: str, dtype: str, tb: TraceBuilder, vocab: int, page_size: int = 16,
-              max_tokens: int = None, subprocess_mode: bool = False) -> Dict[Tuple[str, int], np.ndarray]:
-    """(request, position) -> logits row."""
+              max_tokens: int = None, subprocess_mode: bool = False,
+              max_live: int = 8) -> Dict[Tuple[str, int], np.ndarray]:
+    """(request, position) -> logits row.  ``max_live``: the session's state slots (None: the program's own
+    default)."""
     out_dir = tempfile.mkdtemp(prefix="trace_out_")
     text = "".join(json.dumps(s) + "\n" for s in tb.steps)
     argv = ["--model", model_dir, "--dtype", dtype, "--out", out_dir, "--max-tokens",
             str(max_tokens if max_tokens is not None else tb.peak), "--block-size", str(page_size)]
+    if max_live is not None:
+        argv += ["--max-live", str(max_live)]
     if subprocess_mode:
         proc = subprocess.run([os.path.join(ROOT, "bin", "trace_run")] + argv, input=text.encode(),
                               stdout=subprocess.PIPE, stderr=subprocess.PIPE, timeout=600)

@@ -38,6 +38,8 @@ def test_a_parallel_mixer_keeps_pages_and_two_states():
     assert lay.groups[g2] == StateNeed((2, 16, 48)) and lay.owners[g2] == [2, 4, 6]
     # keys and values of one size: no size of its own for the values
     assert KVPagesNeed(4, 16, 37) in lay.groups
+    # keys and values of two sizes, the larger a size of the tensor-core kernels: rows of that size for both
+    assert KVPagesNeed(2, 64, 5) in build(FV_B).layout.groups and KVPagesNeed(1, 64, 64) in build(FV_B).layout.groups
     # a convolution of one tap keeps an empty tail
     assert StateNeed((0, 128)) in build(FV_B).layout.groups
     assert all(isinstance(g, StateNeed) for g in build(FV_C).layout.groups)

@@ -433,7 +433,7 @@ def test_every_way_of_cutting_gives_the_plain_logits(fv_dirs, name, page, dtype)
                      ("portions", ru.trace_portions(reqs, seed=1)), ("portions b", ru.trace_portions(reqs, seed=4)),
                      ("mixed", ru.trace_mixed(reqs, seed=2, live=4, tail=6)),
                      ("mixed b", ru.trace_mixed(reqs, seed=3, live=3, tail=30))):
-        got = ru.run_trace(fv_dirs[name], dtype, tb, V, page_size=page)
+        got = ru.run_trace(fv_dirs[name], dtype, tb, V, page_size=page, max_live=4)
         compare(got, want, reqs, dtype, f"{name}/{dtype}/page {page}/{what}")
 
 
@@ -478,7 +478,7 @@ def test_the_runner_as_a_program_and_pools_no_larger_than_asked(fv_dirs):
     reqs = make_requests(V, [40, 70, 9, 64, 3, 20], seed=13)
     want = plain_rows(fv_dirs["B"], "float32", reqs)
     tb = ru.trace_mixed(reqs, seed=5, live=4, tail=4)
-    got = ru.run_trace(fv_dirs["B"], "float32", tb, V, page_size=16, subprocess_mode=True)
+    got = ru.run_trace(fv_dirs["B"], "float32", tb, V, page_size=16, subprocess_mode=True, max_live=None)
     compare(got, want, reqs, "float32", "child process")
 
 
