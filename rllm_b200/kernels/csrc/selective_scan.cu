@@ -92,7 +92,8 @@ selective_scan_kernel(const T* xc, const float* dt_raw, const TW* dt_bias, const
   const bool mine = c < E;
   float A[NMAX];
 #pragma unroll
-  for (int n = 0; n < NMAX; ++n) A[n] = (mine && n < N) ? -expf(to_f32(a_log[(size_t)c * N + n])) : 0.f;
+  // A times log2(e): the decay exp(dt A) is then one exp2 (a single special-function instruction)
+  for (int n = 0; n < NMAX; ++n) A[n] = (mine && n < N) ? -expf(to_f32(a_log[(size_t)c * N + n])) * 1.4426950408889634f : 0.f;
   const float bias = mine ? to_f32(dt_bias[c]) : 0.f, dsk = mine ? to_f32(dskip[c]) : 0.f;
   pdl_wait();
   pdl_launch();
@@ -114,30 +115,53 @@ selective_scan_kernel(const T* xc, const float* dt_raw, const TW* dt_bias, const
 #pragma unroll
   for (int n = 0; n < NMAX; ++n) S[n] = (MODE != 1 && mine && n < N) ? sp[(size_t)n * E + c] : 0.f;
   float dt_sum = 0.f;
+  // The next eight tokens' values are fetched into registers before this eight's arithmetic starts, so that
+  // the loads' latency lies behind it.
+  constexpr int PB = (SS_TOKENS * NMAX + SS_THREADS - 1) / SS_THREADS;
+  T px[SS_TOKENS], pz[SS_TOKENS], pb[PB], pc[PB];
+  float pd[SS_TOKENS];
+  auto fetch = [&](int tb) {
+    const int cnt = min(SS_TOKENS, t1 - tb);
+#pragma unroll
+    for (int u = 0; u < PB; ++u) {
+      const int e = threadIdx.x + u * SS_THREADS;
+      const int tt = e / NMAX, n = e - tt * NMAX;
+      const bool on = e < SS_TOKENS * NMAX && tt < cnt && n < N;
+      const T* row = bc + (size_t)(tb + tt) * bc_stride;
+      pb[u] = on ? row[b_off + n] : from_f32<T>(0.f);
+      pc[u] = on ? row[c_off + n] : from_f32<T>(0.f);
+    }
+#pragma unroll
+    for (int tt = 0; tt < SS_TOKENS; ++tt) {
+      const bool on = mine && tt < cnt;
+      const size_t t = (size_t)(tb + tt);
+      px[tt] = on ? xc[t * E + c] : from_f32<T>(0.f);
+      pd[tt] = on ? dt_raw[t * E + c] : 0.f;
+      pz[tt] = (on && MODE != 1) ? z[t * z_stride + c] : from_f32<T>(0.f);
+    }
+  };
+  fetch(t0);
   for (int tb = t0; tb < t1; tb += SS_TOKENS) {
     const int cnt = min(SS_TOKENS, t1 - tb);
     __syncthreads();
-    for (int e = threadIdx.x; e < SS_TOKENS * NMAX; e += SS_THREADS) {
-      const int tt = e / NMAX, n = e - tt * NMAX;
-      float bv = 0.f, cv = 0.f;
-      if (tt < cnt && n < N) {
-        const T* row = bc + (size_t)(tb + tt) * bc_stride;
-        bv = to_f32(row[b_off + n]);
-        cv = to_f32(row[c_off + n]);
+#pragma unroll
+    for (int u = 0; u < PB; ++u) {
+      const int e = threadIdx.x + u * SS_THREADS;
+      if (e < SS_TOKENS * NMAX) {
+        (&Bs[0][0])[e] = to_f32(pb[u]);
+        (&Cs[0][0])[e] = to_f32(pc[u]);
       }
-      Bs[tt][n] = bv;
-      Cs[tt][n] = cv;
     }
     float xv[SS_TOKENS], dv[SS_TOKENS], zv[SS_TOKENS];
 #pragma unroll
     for (int tt = 0; tt < SS_TOKENS; ++tt) {
       const bool on = mine && tt < cnt;
-      const size_t t = (size_t)(tb + tt);
-      xv[tt] = on ? to_f32(xc[t * E + c]) : 0.f;
-      dv[tt] = on ? ss_softplus(dt_raw[t * E + c] + bias) : 0.f;
-      zv[tt] = (on && MODE != 1) ? to_f32(z[t * z_stride + c]) : 0.f;
+      xv[tt] = to_f32(px[tt]);
+      dv[tt] = on ? ss_softplus(pd[tt] + bias) : 0.f;
+      zv[tt] = to_f32(pz[tt]);
     }
     __syncthreads();
+    if (tb + SS_TOKENS < t1) fetch(tb + SS_TOKENS);
 #pragma unroll
     for (int tt = 0; tt < SS_TOKENS; ++tt) {
       if (tt < cnt) {
@@ -145,7 +169,7 @@ selective_scan_kernel(const T* xc, const float* dt_raw, const TW* dt_bias, const
         float y = 0.f;
 #pragma unroll
         for (int n = 0; n < NMAX; ++n) {
-          S[n] = fmaf(expf(dt * A[n]), S[n], dx * Bs[tt][n]);
+          S[n] = fmaf(exp2f(dt * A[n]), S[n], dx * Bs[tt][n]);
           if (MODE != 1) y = fmaf(S[n], Cs[tt][n], y);
         }
         dt_sum += dt;
