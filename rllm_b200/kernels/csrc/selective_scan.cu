@@ -57,6 +57,69 @@ causal_conv_kernel(const T* x, int stride, const TW* w, const TW* bias, float* t
   }
 }
 
+// Up to CV_TAPS taps: one thread takes a channel and CV_RUN consecutive tokens of the step and keeps the
+// last taps - 1 inputs in registers, so that a token costs one load (the window is fetched anew where the
+// run crosses into another sequence).  Weights and window are held right-aligned: entry CV_TAPS - 1 is the
+// current token's.
+#define CV_TAPS 8
+#define CV_RUN 8
+template <typename T, typename TW>
+__global__ void __launch_bounds__(128)
+causal_conv_run_kernel(const T* x, int stride, const TW* w, const TW* bias, float* tail, const int* q_start,
+                       const int* token_seq, const int* slots, int num_slots, T* out, int E, int taps, int T_tokens,
+                       int* err) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const bool mine = c < E;
+  float wv[CV_TAPS];
+#pragma unroll
+  for (int k = 0; k < CV_TAPS; ++k) wv[CV_TAPS - 1 - k] = (mine && k < taps) ? to_f32(w[(size_t)c * taps + taps - 1 - k]) : 0.f;
+  const float b = mine ? to_f32(bias[c]) : 0.f;
+  pdl_wait();
+  pdl_launch();
+  if (!mine) return;
+  float win[CV_TAPS - 1];
+  int cur = -1, first = 0, qlen = 0;
+  float* tl = nullptr;
+  const int t_end = min(T_tokens, (int)(blockIdx.y + 1) * CV_RUN);
+  for (int t = blockIdx.y * CV_RUN; t < t_end; ++t) {
+    const int s = token_seq[t];
+    if (s != cur) {
+      cur = s;
+      first = q_start[s];
+      qlen = q_start[s + 1] - first;
+      const int slot = slots[s];
+      if (slot < 0 || slot >= num_slots) {
+        atomicOr(err, 8);
+        return;
+      }
+      tl = tail + (size_t)slot * (taps - 1) * E + c;
+      const int li = t - first;
+#pragma unroll
+      for (int k = 1; k < CV_TAPS; ++k) {              // the input k places back
+        float v = 0.f;
+        if (k <= taps - 1) {
+          const int src = li - k;
+          v = (src >= 0) ? to_f32(x[(size_t)(first + src) * stride + c]) : tl[(size_t)(taps - 1 + src) * E];
+        }
+        win[CV_TAPS - 1 - k] = v;
+      }
+    }
+    const float xv = to_f32(x[(size_t)t * stride + c]);
+    float acc = b;
+#pragma unroll
+    for (int j = 0; j < CV_TAPS - 1; ++j) acc = fmaf(wv[j], win[j], acc);
+    acc = fmaf(wv[CV_TAPS - 1], xv, acc);
+    out[(size_t)t * E + c] = from_f32<T>(ss_silu(acc));
+#pragma unroll
+    for (int j = 0; j < CV_TAPS - 2; ++j) win[j] = win[j + 1];
+    win[CV_TAPS - 2] = xv;
+    if (qlen == 1) {                     // the only reader of this sequence's tail: move it on by one input
+      for (int k = 0; k + 1 < taps - 1; ++k) tl[(size_t)k * E] = tl[(size_t)(k + 1) * E];
+      if (taps > 1) tl[(size_t)(taps - 2) * E] = xv;
+    }
+  }
+}
+
 // sequences that brought more than one token: the tail becomes their last taps - 1 inputs
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -227,10 +290,17 @@ RLLM_EXPORT int rllm_causal_conv(const void* x, int stride, int dtype, const voi
   if (T <= 0) return 0;
   if (E <= 0 || taps <= 0 || taps > 64 || num_slots <= 0) return RLLM_E_BADARG;
   const long long total = (long long)T * E;
-  RLLM_DISPATCH_DTYPE(dtype, TT, RLLM_DISPATCH_DTYPE(w_dtype, TW,
-    (rllm_launch_pdl(causal_conv_kernel<TT, TW>, dim3((unsigned)((total + 255) / 256)), dim3(256), (size_t)0, stream,
-                     (const TT*)x, stride, (const TW*)w, (const TW*)bias, tail, q_start, token_seq, slots, num_slots,
-                     (TT*)out, E, taps, total, err))));
+  if (taps <= CV_TAPS && (T + CV_RUN - 1) / CV_RUN <= 65535) {
+    RLLM_DISPATCH_DTYPE(dtype, TT, RLLM_DISPATCH_DTYPE(w_dtype, TW,
+      (rllm_launch_pdl(causal_conv_run_kernel<TT, TW>, dim3((unsigned)((E + 127) / 128), (unsigned)((T + CV_RUN - 1) / CV_RUN)),
+                       dim3(128), (size_t)0, stream, (const TT*)x, stride, (const TW*)w, (const TW*)bias, tail, q_start,
+                       token_seq, slots, num_slots, (TT*)out, E, taps, T, err))));
+  } else {
+    RLLM_DISPATCH_DTYPE(dtype, TT, RLLM_DISPATCH_DTYPE(w_dtype, TW,
+      (rllm_launch_pdl(causal_conv_kernel<TT, TW>, dim3((unsigned)((total + 255) / 256)), dim3(256), (size_t)0, stream,
+                       (const TT*)x, stride, (const TW*)w, (const TW*)bias, tail, q_start, token_seq, slots, num_slots,
+                       (TT*)out, E, taps, total, err))));
+  }
   if (any_long && taps > 1) {
     if (num_seqs > 65535) return RLLM_E_UNSUPPORTED;
     RLLM_DISPATCH_DTYPE(dtype, TT,

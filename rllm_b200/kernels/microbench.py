@@ -7,6 +7,9 @@
     python -m rllm_b200.kernels.microbench latent_attention --tokens 2048 --heads 16 --kv-rank 512 --rot-dim 64
     python -m rllm_b200.kernels.microbench latent_attention --batch 8 --context 4096 --tokens 1 ...
     python -m rllm_b200.kernels.microbench routed_experts --rows 2048 --experts 32 --top 4 --intermediate 1024
+    python -m rllm_b200.kernels.microbench lightning_scan --tokens 2048 --heads 16 --head-dim 128 --v-dim 128
+    python -m rllm_b200.kernels.microbench selective_scan --tokens 2048 --channels 4096 --state 16
+    python -m rllm_b200.kernels.microbench streams --tokens 2048 --hidden 2048 --streams 4
 
 Sizes default to the Llama-3.2-1B shape (32 heads, 8 kv heads, head 64, hidden
 2048, intermediate 8192).  Times are CUDA-event times over ``--iters`` launches
@@ -213,10 +216,83 @@ def gemm_tcgen05(args) -> None:
     ops.check_gemm_errors(torch.device(DEV))
 
 
+def _one_sequence(T, batch):
+    """(q_start, token_seq, slots, number of sequences, longest): one portion of T tokens, or ``batch``
+    sequences of one token each when T == 1."""
+    S = batch if T == 1 else 1
+    per = 1 if T == 1 else T
+    q_start = torch.arange(0, S * per + 1, per, dtype=torch.int32, device=DEV)
+    token_seq = torch.arange(S, dtype=torch.int32, device=DEV).repeat_interleave(per)
+    return q_start, token_seq, torch.arange(S, dtype=torch.int32, device=DEV), S, per
+
+
+def lightning_scan(args) -> None:
+    """The lightning-attention recurrence over one prompt portion, or one token of ``--batch`` sequences."""
+    heads, d, dv = args.heads, args.head_dim, args.v_dim or args.head_dim
+    q_start, _, slots, S, per = _one_sequence(args.tokens, args.batch)
+    T, qk = S * per, heads * d
+    bufs = [torch.randn(T, 2 * qk + 2 * heads * dv, device=DEV).bfloat16() for _ in range(4)]
+    decay = torch.linspace(0.9, 0.999, heads, device=DEV)
+    state = torch.zeros(S, heads, d, dv, device=DEV)
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+
+    def run(i):
+        a = bufs[i % 4]
+        ops.lightning_scan(a[:, :qk], a[:, qk:2 * qk], a[:, 2 * qk:2 * qk + heads * dv], decay, state, q_start, slots,
+                           S, err, max_q_len=per)
+    us = time_us(run, args.iters)
+    moved = T * heads * (4 * d + 6 * dv) + 8 * S * heads * d * dv
+    print(f"lightning_scan tokens {T} ({S} sequences) heads {heads} x {d} x {dv}: {us:.1f} us, {moved / us / 1e3:.0f} GB/s "
+          f"of rows and state, {4.0 * T * heads * d * dv / us / 1e6:.2f} TFLOP/s float32")
+
+
+def selective_scan(args) -> None:
+    """The convolution and the selective recurrence over one prompt portion, or one token of ``--batch`` sequences."""
+    E, N, R = args.channels, args.state, max(1, args.channels // 32)
+    q_start, token_seq, slots, S, per = _one_sequence(args.tokens, args.batch)
+    T = S * per
+    xz = [torch.randn(T, 2 * E, device=DEV).bfloat16() for _ in range(4)]
+    proj = torch.randn(T, R + 2 * N, device=DEV).bfloat16()
+    dt_raw = torch.randn(T, E, device=DEV)
+    small = lambda *shape: torch.randn(*shape, device=DEV).bfloat16()
+    w_conv, b_conv, dt_b, a_log, dskip = small(E, 4), small(E), small(E), small(E, N), small(E)
+    state, tail = torch.zeros(S, N, E, device=DEV), torch.zeros(S, 3, E, device=DEV)
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    keep = {}
+
+    def conv(i):
+        keep["c"] = ops.causal_conv(xz[i % 4][:, :E], w_conv, b_conv, tail, q_start, token_seq, slots, S, per > 1, err)
+
+    def scan(i):
+        ops.selective_scan(keep["c"], dt_raw, dt_b, proj, R, R + N, a_log, dskip, xz[i % 4][:, E:], state, q_start, slots,
+                           S, err, max_q_len=per)
+    us = time_us(conv, args.iters)
+    print(f"causal_conv tokens {T} channels {E} taps 4: {us:.1f} us, {4.0 * T * E / us / 1e3:.0f} GB/s")
+    us = time_us(scan, args.iters)
+    print(f"selective_scan tokens {T} ({S} sequences) channels {E} states {N}: {us:.1f} us, "
+          f"{(10.0 * T * E + 8.0 * S * N * E) / us / 1e3:.0f} GB/s of rows and state")
+
+
+def streams(args) -> None:
+    """The write-back into all residual streams with the next read and its norm."""
+    S, T, H = args.streams, args.tokens, args.hidden
+    xs = [torch.randn(S, T, H, device=DEV) for _ in range(3)]
+    y = torch.randn(T, H, device=DEV).bfloat16()
+    vec = lambda n: torch.randn(n, device=DEV)
+    mix, write, read, scale = torch.randn(S, S, device=DEV), vec(S), vec(S), vec(H).bfloat16()
+    norm = (torch.tensor([0.5], device=DEV), vec(H).bfloat16(), vec(H).bfloat16())
+
+    def run(i):
+        ops.streams_write(xs[i % 3], y, scale, mix, write, next_read=read, norm=norm)
+    us = time_us(run, args.iters)
+    print(f"streams_write {S} streams x {T} x {H}: {us:.1f} us, {(8.0 * S + 4.0) * T * H / us / 1e3:.0f} GB/s")
+
+
 def main(argv=None) -> int:
     p = argparse.ArgumentParser(prog="python -m rllm_b200.kernels.microbench", description=__doc__.split("\n\n")[0])
     p.add_argument("kernel", choices=["attention_decode", "attention_prefill", "gemm_small_m", "gemm_tcgen05",
-                                      "latent_attention", "routed_experts"])
+                                      "latent_attention", "routed_experts", "lightning_scan", "selective_scan",
+                                      "streams"])
     p.add_argument("--batch", type=int, default=8)
     p.add_argument("--context", type=int, default=4096)
     p.add_argument("--tokens", type=int, default=2048)
@@ -231,6 +307,10 @@ def main(argv=None) -> int:
     p.add_argument("--kv-rank", type=int, default=512, help="latent_attention: values of a cached row")
     p.add_argument("--rot-dim", type=int, default=64, help="latent_attention: the rows' rotated key part")
     p.add_argument("--window", type=int, default=0, help="latent_attention: keys a query sees (0: all)")
+    p.add_argument("--v-dim", type=int, default=0, help="lightning_scan: a value head's size (0: --head-dim)")
+    p.add_argument("--channels", type=int, default=4096, help="selective_scan: inner channels")
+    p.add_argument("--state", type=int, default=16, help="selective_scan: states a channel")
+    p.add_argument("--streams", type=int, default=4, help="streams: residual streams")
     p.add_argument("--experts", type=int, default=32)
     p.add_argument("--top", type=int, default=4)
     p.add_argument("--variant", choices=["plain", "residual", "rstd"], default="plain",
@@ -245,7 +325,8 @@ def main(argv=None) -> int:
         return 1
     {"attention_decode": attention_decode, "attention_prefill": attention_prefill,
      "gemm_small_m": gemm_small_m, "gemm_tcgen05": gemm_tcgen05, "latent_attention": latent_attention,
-     "routed_experts": routed_experts}[args.kernel](args)
+     "routed_experts": routed_experts, "lightning_scan": lightning_scan, "selective_scan": selective_scan,
+     "streams": streams}[args.kernel](args)
     return 0
 
 

@@ -135,7 +135,7 @@ def test_lightning_scan_carries_its_state_across_cuts_and_slots(dtype, heads, d,
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("taps", [1, 2, 4, 7])
+@pytest.mark.parametrize("taps", [1, 2, 4, 7, 9])
 def test_the_convolution_reads_its_tail_and_moves_it_on(dtype, taps):
     """A sequence fed as 1 + 2 + 1 + 9 + 1 tokens beside others, against the convolution of the whole
     sequence: the last taps - 1 inputs travel in the state, also when a step brings fewer than that."""
