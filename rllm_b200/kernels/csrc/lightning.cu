@@ -29,7 +29,7 @@ __device__ __forceinline__ float lt_silu(float v) { return v / (1.0f + expf(-v))
 // mode 0: whole portion from the slot's state, state written back
 // mode 1: one chunk from a zero start, end state to work[chunk], no output
 // mode 2: one chunk from work[chunk], output, nothing written back
-// NS: slices of d (a power of two up to 16; d <= 8 NS); thread = slice + NS * (tile of columns)
+// NS: slices of d (a power of two up to 32; d <= 8 NS); thread = slice + NS * (tile of columns)
 template <typename T, int NS, int MODE>
 __global__ void __launch_bounds__(256)
 lightning_kernel(const T* q, const T* k, const T* v, int stride, const float* decay, float* state, float* work,
@@ -280,7 +280,7 @@ RLLM_EXPORT int rllm_lightning_scan(const void* q, const void* k, const void* v,
   if (num_seqs <= 0) return 0;
   if (heads <= 0 || d <= 0 || dv <= 0 || num_slots <= 0 || max_chunks < 0) return RLLM_E_BADARG;
   if (max_chunks > 0 && !work) return RLLM_E_BADARG;
-  if (d > 128) return RLLM_E_UNSUPPORTED;               // sixteen slices of eight rows: the partners of a sum are one half-warp
+  if (d > 256) return RLLM_E_UNSUPPORTED;               // 32 slices of eight rows: the partners of a sum are one warp
   if ((long long)num_seqs * (max_chunks > 0 ? max_chunks : 1) > 65535) return RLLM_E_UNSUPPORTED;
 #define LT_GO(T_, NS_)                                                                                          \
   lightning_launch<T_, NS_>((const T_*)q, (const T_*)k, (const T_*)v, stride, decay, state, work, q_start, slots, \
@@ -290,7 +290,8 @@ RLLM_EXPORT int rllm_lightning_scan(const void* q, const void* k, const void* v,
     else if (d <= 16) LT_GO(TT, 2);
     else if (d <= 32) LT_GO(TT, 4);
     else if (d <= 64) LT_GO(TT, 8);
-    else LT_GO(TT, 16);
+    else if (d <= 128) LT_GO(TT, 16);
+    else LT_GO(TT, 32);
   });
 #undef LT_GO
   RLLM_LAUNCH_CHECK();

@@ -39,8 +39,8 @@ class LightningAttention(Mixer):
         self.decay = tuple(float(v) for v in p["decay"])
         if len(self.decay) != self.heads:
             raise ValueError(f"lightning_attention: {len(self.decay)} decays for {self.heads} heads")
-        if self.d > 128:
-            raise ValueError(f"lightning_attention: head_dim {self.d}; the scan kernel keeps up to 128 a column")
+        if self.d > 256:
+            raise ValueError(f"lightning_attention: head_dim {self.d}; the scan kernel takes up to 256")
         names = dict(p.get("tensor_names") or ())
         if sorted(names) != sorted(_KEYS):
             raise ValueError(f"a lightning_attention spec names its tensors: tensor_names with the keys {_KEYS}")

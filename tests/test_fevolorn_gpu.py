@@ -107,7 +107,7 @@ def _lightning_plain(q, k, v, decay, state, lens, slots):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("heads,d,dv,lens", [(3, 20, 24, [1, 2, 37]), (1, 64, 128, [5, 1, 1]), (5, 8, 70, [140, 3, 129]),
-                                             (2, 100, 16, [300, 1, 64])])
+                                             (2, 100, 16, [300, 1, 64]), (1, 200, 40, [70, 2, 1])])
 def test_lightning_scan_carries_its_state_across_cuts_and_slots(dtype, heads, d, dv, lens):
     """Sequences of unequal length in one launch (the long ones go through the chunked form), one of them
     continuing from a state that an earlier call left; slots in another order than the sequences; a decay
