@@ -412,7 +412,7 @@ def fasulix(layers, width, heads, dim, rot, vdim, q_rank, kv_rank, gru, experts,
 def fevolorn(layers, width, streams, lheads, ldim, lvdim, heads, kv_heads, dim, vdim, window, inner, state, dt_rank,
              experts, top, ff, shared, dense, vocab):
     """layers of the pattern [lightning + dense, parallel + experts, lightning + experts, parallel + experts]."""
-    moe = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top, "scale": 2.5},
+    moe = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top, "scale": 2.0},
            "shared": {"ff": shared}}
     lightning = {"heads": lheads, "dim": ldim, "vdim": lvdim,
                  "decay": [1.0 - 2.0 ** (-5.0 - 3.0 * h / max(1, lheads - 1)) for h in range(lheads)]}

@@ -44,7 +44,7 @@ FV_B = {
     "layers": [
         {"type": "lightning", "mixer": {"heads": 1, "dim": 64, "vdim": 128, "decay": [0.97]},
          "mlp": _moe(2, 1, 64, 1.0, shared=64)},
-        {"type": "parallel", "mixer": _par(4, 2, 64, 32, 0.125, 5, 128, 16, 16, 1), "mlp": {"kind": "dense", "ff": 192}},
+        {"type": "parallel", "mixer": _par(4, 2, 64, 32, 0.11, 5, 128, 16, 16, 1), "mlp": {"kind": "dense", "ff": 192}},
         {"type": "parallel", "mixer": _par(2, 1, 32, 64, 0.2, 64, 64, 32, 8, 4), "mlp": _moe(8, 2, 32, 2.0)},
     ],
 }
