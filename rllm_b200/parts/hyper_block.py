@@ -18,6 +18,9 @@ the next layer's mixer) and the norm on that read are one kernel where the norm
 needs no statistics (``elementwise()`` of the norm part); another norm runs as a
 kernel of its own on the float32 read.
 
+A caller that puts a list under ``ctx.extras["residual_trace"]`` gets the sum of the streams after every
+layer run appended to it (float32 [T, H], from the layer's last kernel): what the tests compare layer by layer.
+
 norms: two (before the mixer, before the feed-forward).  params: hidden_size,
 streams, tensor_names (keys "read1", "mix1", "write1", "read2", "mix2", "write2",
 and optionally "scale1", "scale2": names below the layer's prefix).
