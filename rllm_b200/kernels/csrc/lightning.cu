@@ -17,6 +17,7 @@
 // chunk c + end-from-zero of chunk c, in order, and the sequence's new state), then every chunk
 // walks its tokens from its start.  Results differ from the plain walk by rounding only.
 #include "common.cuh"
+#include "lightning_mma.cuh"
 #include <math.h>
 
 #define LT_TOKENS 8
@@ -232,12 +233,21 @@ lightning_chain_kernel(const float* decay, float* state, float* work, const int*
   float* sp = state + ((size_t)slot * heads + h) * d * dv + e;
   float cur = *sp;
   const int chunks = (len + LT_CHUNK - 1) / LT_CHUNK;
-  for (int c = 0; c < chunks; ++c) {
-    float* wp = work + (((size_t)s * max_chunks + c) * heads + h) * d * dv + e;
-    const float z = *wp;
-    *wp = cur;
-    const int n = min(LT_CHUNK, len - c * LT_CHUNK);
-    cur = fmaf(n == LT_CHUNK ? full : powf(lam, (float)n), cur, z);
+  float* w0 = work + ((size_t)s * max_chunks * heads + h) * d * dv + e;
+  const size_t step = (size_t)heads * d * dv;
+  // eight chunks' end states are fetched before the chain runs over them (the loads do not depend on it)
+  for (int c0 = 0; c0 < chunks; c0 += 8) {
+    float z[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) z[u] = (c0 + u < chunks) ? w0[(size_t)(c0 + u) * step] : 0.f;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      if (c0 + u < chunks) {
+        w0[(size_t)(c0 + u) * step] = cur;
+        const int n = min(LT_CHUNK, len - (c0 + u) * LT_CHUNK);
+        cur = fmaf(n == LT_CHUNK ? full : powf(lam, (float)n), cur, z[u]);
+      }
+    }
   }
   *sp = cur;
 }
@@ -273,6 +283,13 @@ static int lightning_launch(const T* q, const T* k, const T* v, int stride, cons
 // num_seqs * max_chunks * heads * d * dv floats.
 RLLM_EXPORT int rllm_lightning_chunk() { return LT_CHUNK; }
 
+// RLLM_LIGHTNING=simt keeps the chunk passes on the CUDA cores (for tests and comparisons)
+static inline bool lightning_mma_disabled() {
+  static int off = -1;
+  if (off < 0) { const char* e = getenv("RLLM_LIGHTNING"); off = (e && e[0] == 's') ? 1 : 0; }
+  return off == 1;
+}
+
 RLLM_EXPORT int rllm_lightning_scan(const void* q, const void* k, const void* v, int stride, int dtype,
                                     const float* decay, float* state, float* work, const int* q_start,
                                     const int* slots, int num_slots, int num_seqs, int max_chunks, float* out,
@@ -282,6 +299,25 @@ RLLM_EXPORT int rllm_lightning_scan(const void* q, const void* k, const void* v,
   if (max_chunks > 0 && !work) return RLLM_E_BADARG;
   if (d > 256) return RLLM_E_UNSUPPORTED;               // 32 slices of eight rows: the partners of a sum are one warp
   if ((long long)num_seqs * (max_chunks > 0 ? max_chunks : 1) > 65535) return RLLM_E_UNSUPPORTED;
+  static_assert(LT_CHUNK == LTC_CHUNK, "the chain kernel serves both forms of the chunk passes");
+  if (dtype == RLLM_DT_BF16 && max_chunks > 0 && !lightning_mma_disabled() && stride % 2 == 0) {
+    // long portions of bfloat16 activations: the chunk passes on the tensor cores, where the head's sizes are built
+    auto chain = [&]() {
+      rllm_launch_pdl(lightning_chain_kernel, dim3(heads, num_seqs, (d * dv + 255) / 256), dim3(256), (size_t)0, stream,
+                      decay, state, work, q_start, slots, num_slots, max_chunks, heads, d, dv);
+    };
+    bool done = false;
+#define LTC_GO(D_, DV_)                                                                                          \
+  if (!done && d == D_ && dv == DV_)                                                                             \
+    done = ltc_launch<D_, DV_>((const bf16*)q, (const bf16*)k, (const bf16*)v, stride, decay, work, q_start,     \
+                               num_seqs, max_chunks, out, heads, stream, chain)
+    LTC_GO(32, 64); LTC_GO(32, 128); LTC_GO(64, 64); LTC_GO(64, 128); LTC_GO(128, 64); LTC_GO(128, 128);
+#undef LTC_GO
+    if (done) {
+      RLLM_LAUNCH_CHECK();
+      return 0;
+    }
+  }
 #define LT_GO(T_, NS_)                                                                                          \
   lightning_launch<T_, NS_>((const T_*)q, (const T_*)k, (const T_*)v, stride, decay, state, work, q_start, slots, \
                            num_slots, num_seqs, max_chunks, out, heads, d, dv, err, stream)

@@ -271,12 +271,22 @@ selective_chain_kernel(const TW* a_log, float* state, float* work, const float* 
   float* sp = state + (size_t)slot * N * E + e;
   float cur = *sp;
   const int chunks = (len + SS_CHUNK - 1) / SS_CHUNK;
-  for (int k = 0; k < chunks; ++k) {
-    const size_t w = (size_t)s * max_chunks + k;
-    float* wp = work + w * N * E + e;
-    const float zend = *wp;
-    *wp = cur;
-    cur = fmaf(expf(a * work_dt[w * E + c]), cur, zend);
+  // eight chunks' summaries are fetched before the chain runs over them (the loads do not depend on it)
+  for (int k0 = 0; k0 < chunks; k0 += 8) {
+    float zend[8], dts[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const size_t w = (size_t)s * max_chunks + k0 + u;
+      zend[u] = (k0 + u < chunks) ? work[w * N * E + e] : 0.f;
+      dts[u] = (k0 + u < chunks) ? work_dt[w * E + c] : 0.f;
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      if (k0 + u < chunks) {
+        work[((size_t)s * max_chunks + k0 + u) * N * E + e] = cur;
+        cur = fmaf(expf(a * dts[u]), cur, zend[u]);
+      }
+    }
   }
   *sp = cur;
 }

@@ -87,8 +87,9 @@ def test_the_tanh_norm_alone_with_an_add_and_chosen_rows(dtype):
     assert rel(out, torch.tanh(1.3 * s[[7, 2]]) * w.double() + c.double()) <= (1e-6 if dtype == "float32" else 1e-2)
 
 
-def _lightning_plain(q, k, v, decay, state, lens, slots):
-    """state [slots, heads, d, dv] (updated), returns o [T, heads * dv]; float64."""
+def _lightning_plain(q, k, v, decay, state, lens, slots, round_act=False):
+    """state [slots, heads, d, dv] (updated), returns o [T, heads * dv]; float64.  ``round_act``: the
+    activated q, k and v are rounded to bfloat16 (what the tensor-core form of the chunk passes does)."""
     heads, d, dv = state.shape[1:]
     T = q.shape[0]
     out = torch.zeros(T, heads, dv, dtype=F64)
@@ -98,6 +99,8 @@ def _lightning_plain(q, k, v, decay, state, lens, slots):
             S = state[sl, h].clone()
             for t in range(off, off + n):
                 kk, vv, qq = (pv.silu(x[t].double().view(heads, -1)[h]) for x in (k, v, q))
+                if round_act:
+                    kk, vv, qq = (x.float().bfloat16().double() for x in (kk, vv, qq))
                 S = decay[h] * S + torch.outer(kk, vv)
                 out[t, h] = S.t() @ qq
             state[sl, h] = S
@@ -131,6 +134,34 @@ def test_lightning_scan_carries_its_state_across_cuts_and_slots(dtype, heads, d,
     assert int(err.item()) == 0
     assert rel(got, want) <= 2e-6
     assert rel(st, want_state) <= 2e-6
+    assert torch.equal(st[[1, 3, 5]].cpu(), state[[1, 3, 5]])
+
+
+@pytest.mark.parametrize("heads,d,dv,lens,decay", [(2, 32, 64, [200, 3, 129], [1.0, 0.6]), (1, 128, 128, [150, 64, 1], [0.97]),
+                                                   (3, 64, 64, [130, 1, 70], [0.999, 0.05, 0.0]), (2, 128, 64, [65, 257, 2], [0.9, 0.5]),
+                                                   (1, 64, 128, [129, 16, 17], [0.8]), (2, 32, 128, [300, 5, 63], [0.99, 0.7])])
+def test_lightning_chunk_passes_on_the_tensor_cores(heads, d, dv, lens, decay):
+    """Long portions of bfloat16 activations at the head sizes the tensor-core form is built for: chunks of
+    64 with a ragged last one, sequences shorter than a chunk beside them, a state left by an earlier call,
+    decays of one, nearly zero and zero; against the token-by-token recurrence in float64 on the same
+    bfloat16-rounded activations.  Weights, start states and weighted keys pass as value + remainder, so the
+    result keeps float32's digits (nearly: 16 bits of mantissa a factor)."""
+    from rllm_b200.kernels import ops
+    g = torch.Generator().manual_seed(d + dv)
+    T, slots, qk = sum(lens), [4, 0, 2], heads * d
+    a = torch.randn(T, 2 * qk + heads * dv + 6, generator=g).bfloat16()
+    lam = torch.tensor(decay, dtype=torch.float32)
+    state = torch.zeros(6, heads, d, dv)
+    state[0] = torch.randn(heads, d, dv, generator=g)
+    want_state = state.double().clone()
+    want = _lightning_plain(a[:, :qk], a[:, qk:2 * qk], a[:, 2 * qk:2 * qk + heads * dv], lam.double(), want_state, lens,
+                            slots, round_act=True)
+    ad, st, err = a.cuda(), state.cuda(), err_word()
+    got = ops.lightning_scan(ad[:, :qk], ad[:, qk:2 * qk], ad[:, 2 * qk:2 * qk + heads * dv], lam.cuda(), st,
+                             i32([0] + list(np.cumsum(lens))), i32(slots), 3, err, max_q_len=max(lens))
+    assert int(err.item()) == 0
+    assert rel(got, want) <= 3e-5
+    assert rel(st, want_state) <= 3e-5
     assert torch.equal(st[[1, 3, 5]].cpu(), state[[1, 3, 5]])
 
 
