@@ -19,9 +19,11 @@
 template <int D, int DV> struct LtcSmem1 {
   bf16 kh[LTC_CHUNK][D + 8], kl[LTC_CHUNK][D + 8], v[LTC_CHUNK][DV + 8];
 };
-template <int D, int DV> struct LtcSmem2 {
-  bf16 q[LTC_CHUNK][D + 8], k[LTC_CHUNK][D + 8], v[LTC_CHUNK][DV + 8], sh[D][DV + 8], sl[D][DV + 8];
+// pass 2 works on DVB value columns a block (all of them, or half where two blocks then fit an SM)
+template <int D, int DVB> struct LtcSmem2 {
+  bf16 q[LTC_CHUNK][D + 8], k[LTC_CHUNK][D + 8], v[LTC_CHUNK][DVB + 8], sh[D][DVB + 8], sl[D][DVB + 8];
 };
+template <int D, int DV> struct LtcSplit { static constexpr int N = (D > 64 && DV > 64) ? 2 : 1; };
 
 __device__ __forceinline__ float ltc_silu(float v) { return v / (1.0f + expf(-v)); }
 __device__ __forceinline__ uint32_t ltc_pack(bf16 a, bf16 b) {
@@ -86,15 +88,16 @@ __device__ __forceinline__ void ltc_store4(bf16* dst, const float (&o)[4]) {
 }
 
 // a chunk's rows of one projection into shared memory [token][W + 8], activated and rounded
-template <int W>
+// (W columns from column `col0` of the head's HW)
+template <int W, int HW>
 __device__ __forceinline__ void ltc_stage_rows(bf16 (*dst)[W + 8], const bf16* src, int stride, int t0, int n, int h,
-                                               bool wide) {
+                                               int col0, bool wide) {
 #pragma unroll
   for (int e0 = 0; e0 < LTC_CHUNK * W; e0 += LTC_THREADS * 4) {
     const int e = e0 + threadIdx.x * 4;
     const int j = e / W, c = e - j * W;
     float o[4];
-    ltc_fetch4(src + (size_t)(t0 + j) * stride + (size_t)h * W + c, j < n, wide, o);
+    ltc_fetch4(src + (size_t)(t0 + j) * stride + (size_t)h * HW + col0 + c, j < n, wide, o);
     ltc_store4(&dst[j][c], o);
   }
 }
@@ -128,7 +131,7 @@ lightning_mma_pass1_kernel(const bf16* k, const bf16* v, int stride, int wide, c
     ltc_store4(&sm.kh[j][i], hi);
     ltc_store4(&sm.kl[j][i], lo);
   }
-  ltc_stage_rows<DV>(sm.v, v, stride, t0, n, h, wide != 0);
+  ltc_stage_rows<DV, DV>(sm.v, v, stride, t0, n, h, 0, wide != 0);
   __syncthreads();
   // a warp owns DV / 4 value columns and half of the d rows
   constexpr int MT = D / 32, NT = DV / 32;
@@ -176,24 +179,26 @@ template <int D, int DV>
 __global__ void __launch_bounds__(LTC_THREADS)
 lightning_mma_pass2_kernel(const bf16* q, const bf16* k, const bf16* v, int stride, int wide, const float* decay,
                            const float* work, const int* q_start, int max_chunks, float* out, int heads) {
+  constexpr int DVB = DV / LtcSplit<D, DV>::N;
   extern __shared__ __align__(16) unsigned char ltc_raw[];
-  LtcSmem2<D, DV>& sm = *reinterpret_cast<LtcSmem2<D, DV>*>(ltc_raw);
+  LtcSmem2<D, DVB>& sm = *reinterpret_cast<LtcSmem2<D, DVB>*>(ltc_raw);
   pdl_wait();
   pdl_launch();
   const int h = blockIdx.x, s = blockIdx.y / max_chunks, chunk = blockIdx.y % max_chunks;
+  const int cb = blockIdx.z * DVB;                // this block's value columns
   const int t0 = q_start[s] + chunk * LTC_CHUNK;
   const int n = min(LTC_CHUNK, q_start[s + 1] - t0);
   if (n <= 0) return;
   const float l2 = log2f(decay[h]);
-  ltc_stage_rows<D>(sm.q, q, stride, t0, n, h, wide != 0);
-  ltc_stage_rows<D>(sm.k, k, stride, t0, n, h, wide != 0);
-  ltc_stage_rows<DV>(sm.v, v, stride, t0, n, h, wide != 0);
+  ltc_stage_rows<D, D>(sm.q, q, stride, t0, n, h, 0, wide != 0);
+  ltc_stage_rows<D, D>(sm.k, k, stride, t0, n, h, 0, wide != 0);
+  ltc_stage_rows<DVB, DV>(sm.v, v, stride, t0, n, h, cb, wide != 0);
   const float* s0 = work + ((size_t)blockIdx.y * heads + h) * D * DV;      // the chunk's start state [i][c]
 #pragma unroll 8
-  for (int e0 = 0; e0 < D * DV; e0 += LTC_THREADS * 4) {
+  for (int e0 = 0; e0 < D * DVB; e0 += LTC_THREADS * 4) {
     const int e = e0 + threadIdx.x * 4;
-    const int i = e / DV, c = e - i * DV;
-    const float4 x = *(const float4*)(s0 + e);
+    const int i = e / DVB, c = e - i * DVB;
+    const float4 x = *(const float4*)(s0 + (size_t)i * DV + cb + c);
     float hi[4] = {x.x, x.y, x.z, x.w}, lo[4];
 #pragma unroll
     for (int y = 0; y < 4; ++y) {
@@ -207,9 +212,10 @@ lightning_mma_pass2_kernel(const bf16* q, const bf16* k, const bf16* v, int stri
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
   const int r0 = (warp & 3) * 16;                 // this warp's 16 tokens,
-  const int cbase = (warp >> 2) * (DV / 2);       // and its half of the value columns (the pair computes the weights twice)
-  if (r0 >= n) return;
-  constexpr int NT = DV / 16;
+  const int cbase = (warp >> 2) * (DVB / 2);      // and its half of the block's value columns (the weights are computed
+  if (r0 >= n) return;                            // by every warp that needs them)
+  constexpr int NT = DVB / 16;
+  static_assert(NT >= 2 && NT % 2 == 0, "a warp takes pairs of n-tiles");
   float o[NT][4];
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt)
@@ -223,8 +229,8 @@ lightning_mma_pass2_kernel(const bf16* q, const bf16* k, const bf16* v, int stri
 #pragma unroll
     for (int np = 0; np < NT / 2; ++np) {
       uint32_t bh[4], bl[4];
-      ltc_b_t<DV + 8>(bh, &sm.sh[0][0], cbase + np * 16, kk);
-      ltc_b_t<DV + 8>(bl, &sm.sl[0][0], cbase + np * 16, kk);
+      ltc_b_t<DVB + 8>(bh, &sm.sh[0][0], cbase + np * 16, kk);
+      ltc_b_t<DVB + 8>(bl, &sm.sl[0][0], cbase + np * 16, kk);
       tgm_mma(o[2 * np], a, bh[0], bh[1]);
       tgm_mma(o[2 * np + 1], a, bh[2], bh[3]);
       tgm_mma(o[2 * np], a, bl[0], bl[1]);
@@ -280,7 +286,7 @@ lightning_mma_pass2_kernel(const bf16* q, const bf16* k, const bf16* v, int stri
 #pragma unroll
       for (int np = 0; np < NT / 2; ++np) {
         uint32_t b[4];
-        ltc_b_t<DV + 8>(b, &sm.v[0][0], cbase + np * 16, ks * 16);
+        ltc_b_t<DVB + 8>(b, &sm.v[0][0], cbase + np * 16, ks * 16);
         tgm_mma(o[2 * np], ah, b[0], b[1]);
         tgm_mma(o[2 * np + 1], ah, b[2], b[3]);
         tgm_mma(o[2 * np], al, b[0], b[1]);
@@ -290,7 +296,7 @@ lightning_mma_pass2_kernel(const bf16* q, const bf16* k, const bf16* v, int stri
   }
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) {
-    const int c = cbase + nt * 8 + 2 * tq;
+    const int c = cb + cbase + nt * 8 + 2 * tq;
     const int ta = r0 + g, tb = r0 + g + 8;
     if (ta < n) *(float2*)(out + ((size_t)(t0 + ta) * heads + h) * DV + c) = make_float2(o[nt][0], o[nt][1]);
     if (tb < n) *(float2*)(out + ((size_t)(t0 + tb) * heads + h) * DV + c) = make_float2(o[nt][2], o[nt][3]);
@@ -304,7 +310,7 @@ static bool ltc_launch(const bf16* q, const bf16* k, const bf16* v, int stride, 
                        const int* q_start, int num_seqs, int max_chunks, float* out, int heads, cudaStream_t stream,
                        Chain chain) {
   const dim3 grid(heads, num_seqs * max_chunks);
-  const size_t s1 = sizeof(LtcSmem1<D, DV>), s2 = sizeof(LtcSmem2<D, DV>);
+  const size_t s1 = sizeof(LtcSmem1<D, DV>), s2 = sizeof(LtcSmem2<D, DV / LtcSplit<D, DV>::N>);
   static bool allowed = false;
   if (!allowed) {
     cudaFuncSetAttribute(lightning_mma_pass1_kernel<D, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)s1);
@@ -316,7 +322,7 @@ static bool ltc_launch(const bf16* q, const bf16* k, const bf16* v, int stride, 
   rllm_launch_pdl(lightning_mma_pass1_kernel<D, DV>, grid, dim3(LTC_THREADS), s1, stream, k, v, stride, wide, decay, work,
                   q_start, max_chunks, heads);
   chain();
-  rllm_launch_pdl(lightning_mma_pass2_kernel<D, DV>, grid, dim3(LTC_THREADS), s2, stream, q, k, v, stride, wide, decay,
+  rllm_launch_pdl(lightning_mma_pass2_kernel<D, DV>, dim3(grid.x, grid.y, LtcSplit<D, DV>::N), dim3(LTC_THREADS), s2, stream, q, k, v, stride, wide, decay,
                   (const float*)work, q_start, max_chunks, out, heads);
   return true;
 }
